@@ -1,0 +1,191 @@
+// Memory-bound kernels of the step: embedding gather, RMSNorm, the fused per-head
+// norm + rotation + scale + cache write, and the gated activation.
+//
+// Reference formulas: embedding src/qwen.rs:669-672; RMSNorm src/kernels.rs:1385-1392;
+// rotation src/kernels.rs:1521-1548 with inv_freq from src/qwen.rs:529-533; q scale after the
+// rotation src/qwen.rs:737-761; keys cached normed and rotated, values raw src/qwen.rs:775-785;
+// silu(a) * b src/kernels.rs:1416-1426.
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+// x[t, :] = table[tok[t], :] * scale, into the float32 residual stream.
+template <typename W>
+__global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ tok, float* __restrict__ x,
+                                    int hidden, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = tok[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are checked on the host; never read outside
+  const W* row = table + (size_t)id * hidden;
+  float* out = x + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
+}
+
+GB_EXPORT int gb_embed_gather(const void* table, int table_dtype, const int* tok, float* x, int ntok, int hidden,
+                              int vocab, float scale, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == GB_F32)
+    embed_gather_kernel<float><<<ntok, threads, 0, stream>>>((const float*)table, tok, x, hidden, vocab, scale);
+  else if (table_dtype == GB_BF16)
+    embed_gather_kernel<bf16><<<ntok, threads, 0, stream>>>((const bf16*)table, tok, x, hidden, vocab, scale);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// out[r, :] = x[src(r), :] * (mean(x^2) + eps)^-1/2 * w, statistics in float32.
+// rows_index (optional) gathers: src(r) = rows_index[r].
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
+                               const int* __restrict__ rows_index, int n, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* row = x + (size_t)(rows_index ? rows_index[r] : r) * n;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  T* o = out + (size_t)r * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>(row[i] * inv * w[i]);
+}
+
+GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
+                         int n, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  if (out_dtype == GB_F32)
+    rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)out, rows_index, n, eps);
+  else if (out_dtype == GB_BF16)
+    rmsnorm_kernel<bf16><<<rows, threads, 0, stream>>>(x, w, (bf16*)out, rows_index, n, eps);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}
+
+// ------------------------------------------------------------------ per-head norm + rotation + cache write
+// qkv: [ntok, (nh + 2 nkv) * hd], heads in the order q.., k.., v...  One warp per (token, head).
+//   q heads: optional RMSNorm over hd (weight qw), optional rotation of the first `rot` dims at
+//            the token's position, then * q_scale; written back in place.
+//   k heads: optional RMSNorm (weight kw), optional rotation; written back in place and, with
+//            FLAG_CACHE, into the paged key cache.
+//   v heads: with FLAG_CACHE copied into the paged value cache.
+enum { FLAG_NORM = 1, FLAG_ROPE = 2, FLAG_CACHE = 4, FLAG_INPLACE = 8 };
+
+template <typename T>
+__global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int nh, int nkv, int hd, int rot,
+                                            const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                            const float* __restrict__ inv_freq, float q_scale,
+                                            const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                            const int* __restrict__ seq_slot, PagedKV kv, T* __restrict__ kcache,
+                                            T* __restrict__ vcache, int flags) {
+  const int lane = threadIdx.x & 31;
+  const int heads = nh + 2 * nkv;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (long long)ntok * heads) return;
+  const int t = (int)(gw / heads), h = (int)(gw % heads);
+  T* src = qkv + ((size_t)t * heads + h) * hd;
+  const int pos = tok_pos[t];
+  const bool cache = flags & FLAG_CACHE;
+  if (h >= nh + nkv) {  // value head
+    if (!cache) return;
+    T* dst = vcache + kv.row(seq_slot[tok_seq[t]], pos, h - nh - nkv);
+    for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+    return;
+  }
+  const bool is_q = h < nh;
+  if (is_q && !(flags & FLAG_INPLACE)) return;
+  const float* w = is_q ? qw : kw;
+  float inv = 1.f;
+  if (flags & FLAG_NORM) {
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+      const float v = to_f32(src[i]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    inv = 1.0f / sqrtf(ss / (float)hd + eps);
+  }
+  const float scale = is_q ? q_scale : 1.f;
+  T* cdst = (!is_q && cache) ? kcache + kv.row(seq_slot[tok_seq[t]], pos, h - nh) : nullptr;
+  const bool inplace = flags & FLAG_INPLACE;
+  const bool rope = flags & FLAG_ROPE;
+  const int half = rope ? rot / 2 : 0;
+  for (int i = lane; i < half; i += 32) {
+    float a = to_f32(src[i]) * inv, b = to_f32(src[i + half]) * inv;
+    if (flags & FLAG_NORM) {
+      a *= w[i];
+      b *= w[i + half];
+    }
+    const float ang = (float)pos * inv_freq[i];  // float32 product, as the reference
+    float s, c;
+    sincosf(ang, &s, &c);
+    const T ra = from_f32<T>((a * c - b * s) * scale), rb = from_f32<T>((b * c + a * s) * scale);
+    if (inplace) {
+      src[i] = ra;
+      src[i + half] = rb;
+    }
+    if (cdst) {
+      cdst[i] = ra;
+      cdst[i + half] = rb;
+    }
+  }
+  for (int i = 2 * half + lane; i < hd; i += 32) {  // dims that are not rotated
+    float a = to_f32(src[i]) * inv;
+    if (flags & FLAG_NORM) a *= w[i];
+    const T ra = from_f32<T>(a * scale);
+    if (inplace) src[i] = ra;
+    if (cdst) cdst[i] = ra;
+  }
+}
+
+GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, int nkv, int hd, int rot,
+                                      const float* qw, const float* kw, float eps, const float* inv_freq,
+                                      float q_scale, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                                      const int* page_table, int table_width, int page_size, void* kcache,
+                                      void* vcache, int flags, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (rot < 0 || rot > hd || (rot & 1)) return GB_ERR_SIZE;
+  if ((flags & FLAG_NORM) && (!qw || !kw)) return GB_ERR_ARG;
+  if ((flags & FLAG_ROPE) && !inv_freq) return GB_ERR_ARG;
+  PagedKV kv{page_table, table_width, page_size, nkv, hd};
+  const long long warps = (long long)ntok * (nh + 2 * nkv);
+  const int wpb = 4;
+  const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+  if (dtype == GB_F32)
+    head_norm_rope_cache_kernel<float><<<grid, wpb * 32, 0, stream>>>(
+        (float*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
+        (float*)kcache, (float*)vcache, flags);
+  else if (dtype == GB_BF16)
+    head_norm_rope_cache_kernel<bf16><<<grid, wpb * 32, 0, stream>>>(
+        (bf16*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
+        (bf16*)kcache, (bf16*)vcache, flags);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}
+
+// ------------------------------------------------------------------ gated activation
+// out[t, i] = silu(gu[t, i]) * gu[t, inter + i];  silu(a) = a / (1 + exp(-a)).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / inter;
+  const int i = (int)(idx % inter);
+  const float g = to_f32(gu[t * 2 * inter + i]), u = to_f32(gu[t * 2 * inter + inter + i]);
+  out[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+GB_EXPORT int gb_silu_mul(const void* gu, void* out, int dtype, int ntok, int inter, cudaStream_t stream) {
+  const long long total = (long long)ntok * inter;
+  if (total <= 0) return 0;
+  const unsigned grid = (unsigned)((total + 255) / 256);
+  if (dtype == GB_F32)
+    silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+  else if (dtype == GB_BF16)
+    silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inter);
+  else
+    return GB_ERR_DTYPE;
+  return gb_launch_status();
+}

@@ -1,0 +1,177 @@
+"""A model built from a plan: its parts, their weights, and the forward pass over one step.
+
+``DecoderModel`` knows nothing of any architecture: it builds the parts a ``ModelPlan`` names,
+asks them which tensors they want, binds those from a checkpoint (or from tensors given
+directly), and runs the plan's schedule.  Which model class a folder gets is decided by its
+config.json through the architecture registry.
+
+Reference: ``QwenModel::load`` (src/qwen.rs:458-544) and ``forward_impl`` (src/qwen.rs:658-701).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..cache.pool import KVNeed, StateNeed
+from ..config.registry import load_config
+from ..csrc import build
+from ..parts import base as parts_base
+from ..parts.base import StepContext, build_block, build_part, compute_dtype
+from ..parts.plan import ModelPlan
+from ..weights.loader import check_checkpoint, load_checkpoint
+from ..weights.safetensors_io import ModelFiles
+
+
+class DecoderModel:
+    def __init__(self, plan: ModelPlan, compute: str, device):
+        plan.validate()
+        self.plan, self.compute, self.device = plan, compute, torch.device(device)
+        self.act_dtype = compute_dtype(compute)
+        self.embedding = build_part("embedding", plan.embedding, compute)
+        self.blocks = [build_block(ls, compute) for ls in plan.layers]
+        self.final_norm = build_part("norm", plan.final_norm, compute)
+        self.head = build_part("head", plan.head, compute)
+        self.config = None
+        self.ignored_tensors = []
+
+    # ---- parts and the tensors they want
+    def named_parts(self):
+        """(part, its spec) for every part that can hold weights."""
+        yield self.embedding, self.plan.embedding
+        for block, ls in zip(self.blocks, self.plan.layers):
+            specs = {"mixer_norm": ls.mixer_norm, "mixer": ls.mixer, "ffn_norm": ls.ffn_norm, "ffn": ls.ffn}
+            for name, part in block.parts().items():
+                yield part, specs[name]
+        yield self.final_norm, self.plan.final_norm
+        yield self.head, self.plan.head
+
+    def expected_tensors(self) -> Dict[str, tuple]:
+        """{checkpoint tensor name: shape} over all parts."""
+        out = {}
+        for part, spec in self.named_parts():
+            for short, want in part.wants().items():
+                name = spec.tensors.get(short)
+                if name is None:
+                    if want.optional:
+                        continue
+                    raise ValueError(f"{spec.kind}: the plan names no checkpoint tensor for {short!r}")
+                if name in out and tuple(out[name]) != tuple(want.shape):
+                    raise ValueError(f"tensor {name} is wanted with shapes {out[name]} and {want.shape}")
+                out[name] = tuple(want.shape)
+        return out
+
+    def kernel_units(self):
+        units = []
+        for part, _ in self.named_parts():
+            for u in part.kernel_units():
+                if u not in units:
+                    units.append(u)
+        return units
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Gives every part its tensors: matrices in the compute precision, vectors in float32.
+        A matrix stored in 32-bit is rounded to bfloat16 for the bfloat16 engine, as the
+        reference does for its bf16 matmuls (src/safetensors.rs:707-733)."""
+        converted = {}
+
+        def get(name, role):
+            want = torch.float32 if role == "vector" else self.act_dtype
+            key = (name, want)
+            if key not in converted:
+                t = tensors[name]
+                if t.device != self.device:
+                    t = t.to(self.device)
+                converted[key] = t if t.dtype == want else t.to(want)
+            return converted[key]
+
+        for part, spec in self.named_parts():
+            mine = {}
+            for short, want in part.wants().items():
+                name = spec.tensors.get(short)
+                if name is not None and name in tensors:
+                    mine[short] = get(name, want.role)
+            part.load(mine)
+        converted.clear()
+
+    # ---- cache needs of the schedule
+    def cache_needs(self):
+        """[(schedule position, need)] for entries that keep a cache of their own."""
+        needs = []
+        for i, e in enumerate(self.plan.schedule):
+            if e.cache_of is not None:
+                continue
+            need = self.blocks[e.layer].mixer.cache_need()
+            if need is not None:
+                needs.append((i, need))
+        return needs
+
+    # ---- the step
+    def forward(self, ctx: StepContext, tokens: torch.Tensor) -> torch.Tensor:
+        """Runs the step's packed tokens through the schedule; returns the float32 residual
+        stream [T, H] before the final norm."""
+        x = torch.empty((tokens.numel(), self.plan.hidden_size), dtype=torch.float32, device=self.device)
+        self.embedding.forward(ctx, tokens, x)
+        for i, e in enumerate(self.plan.schedule):
+            owner = i if e.cache_of is None else e.cache_of
+            block = self.blocks[e.layer]
+            cache = self._cache_view(ctx, owner)
+            ctx.extras["entry"] = i
+            block.forward(ctx, x, cache, writes_cache=e.cache_of is None)
+        return x
+
+    def _cache_view(self, ctx, owner):
+        binding = ctx.cache.bindings.get(owner)
+        if binding is None:
+            return None
+        if binding.kind == "kv":
+            return ctx.cache.kv(owner)
+        return ctx.cache.state(owner)
+
+    def logits(self, ctx: StepContext, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """float32 logits [len(rows), vocab] at the packed-token rows ``rows`` (int32)."""
+        h = self.final_norm.forward(ctx, x, rows_index=rows)
+        return self.head.forward(ctx, h)
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights a decode step reads (every matrix once; tied tensors once)."""
+        seen, total = set(), 0
+        for part, _ in self.named_parts():
+            for attr in vars(part).values():
+                w = getattr(attr, "weight", None)
+                if isinstance(w, torch.Tensor) and w.data_ptr() not in seen and w.dim() == 2:
+                    seen.add(w.data_ptr())
+                    total += w.numel() * w.element_size()
+        return total
+
+
+def build_model(folder: Optional[str] = None, *, raw_config: Optional[dict] = None,
+                tensors: Optional[Dict[str, torch.Tensor]] = None, dtype: str = "bfloat16",
+                device="cuda:0", compile_kernels: bool = True) -> DecoderModel:
+    """The model of a folder (config.json + safetensors), or of ``raw_config`` with ``tensors``
+    given directly ({checkpoint name: tensor}, e.g. random weights made on the device)."""
+    from .. import models  # noqa: F401  (registers the architectures)
+    from ..config.registry import resolve_architecture
+
+    if folder is not None:
+        arch, cfg = load_config(folder)
+        files = ModelFiles(folder)
+        names = files.names()
+    else:
+        arch = resolve_architecture(raw_config)
+        cfg = arch.config_class.from_dict(raw_config)
+        files, names = None, set(tensors)
+    plan = arch.build_plan(cfg, names)
+    model = DecoderModel(plan, dtype, device)
+    model.config = cfg
+    ignored = getattr(plan, "ignored_tensors", [])
+    expected = model.expected_tensors()
+    if compile_kernels:
+        build.ensure(model.kernel_units())
+    if files is not None:
+        loaded = load_checkpoint(files, expected, ignored, device=model.device)
+    else:
+        check_checkpoint({n: tuple(t.shape) for n, t in tensors.items()}, expected, ignored, where="(given tensors)")
+        loaded = tensors
+    model.bind(loaded)
+    return model

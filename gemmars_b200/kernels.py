@@ -1,0 +1,197 @@
+"""Python faces of the CUDA units: argument checks, then one call into the compiled library.
+
+Every function here works on CUDA tensors only and launches on PyTorch's current stream.  There
+is no CPU or library fallback: a tensor that is not on a CUDA device, or a unit that cannot be
+built, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+OUT_STORE, OUT_ACCUMULATE = 0, 1
+FLAG_NORM, FLAG_ROPE, FLAG_CACHE, FLAG_INPLACE = 1, 2, 4, 8
+MAX_TOP_K = 1024
+
+_ERRORS = {-2: "unsupported element type", -3: "unsupported size", -4: "missing argument"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"element type {dt} is not supported by the CUDA kernels (float32 or bfloat16)")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str):
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERRORS.get(code, 'refused')} (code {code})")
+    raise KernelError(f"{what}: CUDA launch failed with error {code}")
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels of gemmars_b200 run on CUDA tensors only (got a CPU tensor); "
+                              "there is no CPU path")
+
+
+_sigs = {}
+
+
+def _fn(unit: str, name: str, argtypes, defines=()):
+    key = (unit, name, tuple(defines))
+    f = _sigs.get(key)
+    if f is None:
+        lib = build.load(unit, defines)
+        f = getattr(lib, name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _sigs[key] = f
+    return f
+
+
+# --------------------------------------------------------------------------- elementwise
+
+def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, scale: float = 1.0):
+    """out[t] = table[tokens[t]] * scale; out is the float32 residual stream [T, H]."""
+    _cuda(table, tokens, out)
+    assert tokens.dtype == torch.int32 and out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous()
+    f = _fn("elementwise", "gb_embed_gather",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), out.data_ptr(), tokens.numel(),
+             table.shape[1], table.shape[0], scale, _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
+            rows_index: Optional[torch.Tensor] = None):
+    """out[r] = rmsnorm(x[rows_index[r] or r]) * weight.  x float32 [*, n]; weight float32 [n]."""
+    _cuda(x, weight, out, rows_index)
+    assert x.dtype == torch.float32 and weight.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous()
+    n = x.shape[-1]
+    rows = out.numel() // n
+    assert weight.numel() == n and out.shape[-1] == n
+    if rows_index is not None:
+        assert rows_index.dtype == torch.int32 and rows_index.numel() == rows
+    f = _fn("elementwise", "gb_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
+    _check(f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype), _ptr(rows_index), rows, n,
+             eps, _stream()), "rmsnorm")
+
+
+def head_norm_rope_cache(qkv, nh, nkv, hd, rot, q_weight, k_weight, eps, inv_freq, q_scale, tok_pos, tok_seq,
+                         seq_slot, page_table, page_size, kcache, vcache, flags):
+    """Per-head RMSNorm, rotation and scale of q and k in place in ``qkv`` [T, (nh+2nkv)*hd], and
+    the write of k and v into the paged cache; ``flags`` selects the steps."""
+    _cuda(qkv, q_weight, k_weight, inv_freq, tok_pos, tok_seq, seq_slot, page_table, kcache, vcache)
+    assert qkv.is_contiguous() and qkv.shape[-1] == (nh + 2 * nkv) * hd
+    if flags & FLAG_CACHE:
+        assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype and kcache.is_contiguous()
+        assert kcache.shape[1:] == (nkv, page_size, hd)
+    f = _fn("elementwise", "gb_head_norm_rope_cache",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_float,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[0], nh, nkv, hd, rot, _ptr(q_weight), _ptr(k_weight),
+             eps, _ptr(inv_freq), q_scale, tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(),
+             _ptr(page_table), page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache),
+             _ptr(vcache), flags, _stream()), "head_norm_rope_cache")
+
+
+def silu_mul(gu: torch.Tensor, out: torch.Tensor):
+    """out[t, i] = silu(gu[t, i]) * gu[t, I + i]."""
+    _cuda(gu, out)
+    inter = out.shape[-1]
+    assert gu.shape[-1] == 2 * inter and gu.dtype == out.dtype and gu.is_contiguous() and out.is_contiguous()
+    f = _fn("elementwise", "gb_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), out.numel() // inter, inter, _stream()), "silu_mul")
+
+
+# --------------------------------------------------------------------------- matrix products
+
+def gemm_ref(x, w, out, bias=None, accumulate=False):
+    """out = x @ w.T (+ bias), or out += ... (float32 out) with ``accumulate``; CUDA cores, float32
+    accumulation in ascending order of the inner index."""
+    _cuda(x, w, out, bias)
+    assert x.dtype == w.dtype and x.stride(-1) == 1 and out.stride(-1) == 1 and w.is_contiguous()
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (m, n)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+    f = _fn("gemm_ref", "gb_gemm_ref",
+            [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
+             c_longlong, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), dtype_code(x.dtype), _ptr(bias), out.data_ptr(), dtype_code(out.dtype),
+             OUT_ACCUMULATE if accumulate else OUT_STORE, m, n, k, x.stride(0), out.stride(0), _stream()), "gemm_ref")
+
+
+# --------------------------------------------------------------------------- attention
+
+def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None):
+    """Causal grouped-query attention of q [T, nh*hd] (row stride free) over the paged cache."""
+    _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot)
+    nkv, hd = kcache.shape[1], kcache.shape[3]
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and q.dtype == out.dtype == kcache.dtype
+    f = _fn("attention_ref", "gb_attention_ref",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+             c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), dtype_code(q.dtype), kcache.data_ptr(),
+             vcache.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(),
+             tok_seq.data_ptr(), seq_slot.data_ptr(), q.shape[0], nh, window or 0, _stream()), "attention_ref")
+
+
+# --------------------------------------------------------------------------- sampling
+
+def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None):
+    """out[r] = token drawn from logits[r] (float32 [rows, vocab]).  Rows whose temperature is
+    <= 0 (or all rows when ``temperature`` is None) take the first maximum."""
+    _cuda(logits, out, temperature, top_k, top_p, uniform)
+    assert logits.dtype == torch.float32 and logits.stride(-1) == 1 and out.dtype == torch.int32
+    f = _fn("sampling", "gb_sample",
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
+             _ptr(top_p), _ptr(uniform), out.data_ptr(), _stream()), "sample")
+
+
+# --------------------------------------------------------------------------- choices by precision and shape
+
+def gemm_units(compute: str):
+    """The units ``gemm`` may launch for a model computed in ``compute``."""
+    return [("gemm_ref", ())]
+
+
+def gemm(x, w, out, bias=None, accumulate=False):
+    """out = x @ w.T (+ bias) or, with ``accumulate``, out += ...; picks the kernel for the
+    precision and the number of rows."""
+    gemm_ref(x, w, out, bias, accumulate)
+
+
+def attention_units(compute: str, head_dim: int):
+    return [("attention_ref", ())]
+
+
+def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=None):
+    """Attention of the step's queries over the cache; picks the kernel for the precision and
+    for prompts or single tokens."""
+    attention_ref(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, window)

@@ -1,0 +1,120 @@
+"""Causal grouped-query attention over the cache, with an optional RMSNorm per head on q and k,
+a position encoding, an optional window and optional biases.
+
+For one step (src/qwen.rs:704-794): q, k, v = h Wq^T, h Wk^T, h Wv^T (one product against the
+stacked matrix); per head q = norm(q) -> position encoding -> * scale (the scale after the
+rotation, src/qwen.rs:737-761), k = norm(k) -> position encoding; k and v are appended to the
+cache (keys normed and rotated, values raw, src/qwen.rs:775-785); each query sees the keys
+lo..p of its own sequence (src/model.rs:1187-1226); residual += o Wo^T.
+
+All sizes and constants are parameters: hidden_size, num_heads, num_kv_heads, head_dim,
+qk_norm, qk_norm_eps, bias, window, scale (None: head_dim ** -0.5), position (a PartSpec or
+None), has_kv (False for a layer that only reads another layer's cache).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..cache.pool import KVNeed
+from .base import Part, TensorWant, build_part, register_part
+from .linear import Linear
+from .rotary import Rotary
+
+
+class Attention(Part):
+    category = "mixer"
+
+    def __init__(self, spec, compute):
+        super().__init__(spec, compute)
+        p = spec.params
+        self.hidden_size = int(p["hidden_size"])
+        self.num_heads = int(p["num_heads"])
+        self.num_kv_heads = int(p["num_kv_heads"])
+        self.head_dim = int(p["head_dim"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.eps = float(p.get("qk_norm_eps", 1e-6))
+        self.bias = bool(p.get("bias", False))
+        self.window = p.get("window")
+        self.has_kv = bool(p.get("has_kv", True))
+        scale = p.get("scale")
+        self.scale = float(scale) if scale is not None else float(
+            torch.tensor(float(self.head_dim), dtype=torch.float32).pow(-0.5))
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"attention: {self.num_heads} heads are not a multiple of {self.num_kv_heads} kv heads")
+        if self.head_dim % 16 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"attention: head_dim {self.head_dim} is not supported by the kernels "
+                             "(a multiple of 16 from 16 to 256)")
+        pos = p.get("position")
+        self.position = build_part("position", pos, compute) if pos is not None else None
+        self.qkv = self.o = self.q_norm = self.k_norm = None
+
+    # ---- weights
+    def wants(self):
+        h, nh, nkv, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
+        w = {"q": TensorWant((nh * hd, h)), "o": TensorWant((h, nh * hd))}
+        if self.has_kv:
+            w.update({"k": TensorWant((nkv * hd, h)), "v": TensorWant((nkv * hd, h))})
+        if self.qk_norm:
+            w["q_norm"] = TensorWant((hd,), "vector")
+            if self.has_kv:
+                w["k_norm"] = TensorWant((hd,), "vector")
+        if self.bias:
+            w.update({"q_bias": TensorWant((nh * hd,), "vector"), "o_bias": TensorWant((h,), "vector")})
+            if self.has_kv:
+                w.update({"k_bias": TensorWant((nkv * hd,), "vector"), "v_bias": TensorWant((nkv * hd,), "vector")})
+        return w
+
+    def load(self, t):
+        names = ["q", "k", "v"] if self.has_kv else ["q"]
+        bias = torch.cat([t[n + "_bias"] for n in names]) if self.bias else None
+        self.qkv = Linear(torch.cat([t[n] for n in names], dim=0), bias)
+        self.o = Linear(t["o"], t.get("o_bias") if self.bias else None)
+        if self.qk_norm:
+            self.q_norm = t["q_norm"].contiguous()
+            self.k_norm = t["k_norm"].contiguous() if self.has_kv else self.q_norm
+
+    def kernel_units(self):
+        return (kernels.gemm_units(self.compute) + [("elementwise", ())]
+                + kernels.attention_units(self.compute, self.head_dim))
+
+    def cache_need(self):
+        return KVNeed(self.num_kv_heads, self.head_dim, self.window) if self.has_kv else None
+
+    def weight_bytes(self):
+        return self.qkv.bytes() + self.o.bytes()
+
+    # ---- step
+    def forward(self, ctx, h, residual, cache, writes_cache=True):
+        nh, hd = self.num_heads, self.head_dim
+        nkv = self.num_kv_heads if self.has_kv else 0
+        group, kc, vc = cache
+        writes_cache = writes_cache and self.has_kv
+        qkv = self.qkv(h)
+        norm = kernels.FLAG_NORM if self.qk_norm else 0
+        store = kernels.FLAG_CACHE if writes_cache else 0
+        common = (ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, group.page_table, group.page_size,
+                  kc if writes_cache else None, vc if writes_cache else None)
+        if self.position is None or isinstance(self.position, Rotary):
+            rope = kernels.FLAG_ROPE if self.position is not None else 0
+            rot = self.position.rotary_dim if rope else 0
+            inv_freq = self.position.inv_freq(h.device) if rope else None
+            kernels.head_norm_rope_cache(qkv, nh, nkv, hd, rot, self.q_norm, self.k_norm, self.eps, inv_freq,
+                                         self.scale, *common, norm | rope | store | kernels.FLAG_INPLACE)
+        else:
+            # another position encoding: norm, then the part's own apply, then scale and cache write
+            if norm:
+                kernels.head_norm_rope_cache(qkv, nh, nkv, hd, 0, self.q_norm, self.k_norm, self.eps, None, 1.0,
+                                             *common[:5], None, None, norm | kernels.FLAG_INPLACE)
+            t = qkv.shape[0]
+            q_view = qkv[:, :nh * hd].view(t, nh, hd)
+            k_view = qkv[:, nh * hd:(nh + nkv) * hd].view(t, nkv, hd)
+            self.position.apply(ctx, q_view, k_view)
+            kernels.head_norm_rope_cache(qkv, nh, nkv, hd, 0, None, None, self.eps, None, self.scale, *common,
+                                         store | kernels.FLAG_INPLACE)
+        att = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
+        kernels.attention(ctx, qkv[:, :nh * hd], att, nh, kc, vc, group.page_table, group.page_size, self.window)
+        self.o.add_into(att, residual)
+
+
+register_part("mixer", "attention", Attention)

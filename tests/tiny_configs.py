@@ -1,0 +1,30 @@
+"""Two tiny Qwen3 configurations for tests; they differ in every size and option."""
+
+TINY_A = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 192, "vocab_size": 512, "rope_theta": 10000.0,
+    "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": True,
+    "max_position_embeddings": 256, "eos_token_id": 7,
+}
+
+# heads * head_dim = 192 != hidden; sizes that are no power of two; biases; untied head; a window
+# on two of the three layers; two stop tokens.
+TINY_B = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 3,
+    "head_dim": 32, "intermediate_size": 160, "vocab_size": 1000, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-5, "attention_bias": True, "tie_word_embeddings": False,
+    "max_position_embeddings": 512, "eos_token_id": [3, 11],
+    "use_sliding_window": True, "sliding_window": 40,
+    "layer_types": ["sliding_attention", "full_attention", "sliding_attention"],
+}
+
+# A third shape for spot checks: one kv head, a wider head, partial rotation.
+TINY_C = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 1, "hidden_size": 80, "num_attention_heads": 5, "num_key_value_heads": 1,
+    "head_dim": 48, "intermediate_size": 112, "vocab_size": 301, "rope_theta": 50000.0,
+    "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": False,
+    "partial_rotary_factor": 0.5, "max_position_embeddings": 1024,
+}
