@@ -111,7 +111,7 @@ class KVGroup:
     """Storage of the layers that share one ``KVNeed``.
 
     ``k`` and ``v``: ``[layers, pages + 1, kv_heads, page_size, head_dim]``.
-    ``page_table``: ``[slots, table_width]`` int32; position ``p`` of the sequence in slot ``s``
+    ``page_table``: ``[slots + 1, table_width]`` int32; position ``p`` of the sequence in slot ``s``
     lives in page ``page_table[s, (p // page_size) % table_width]`` at offset ``p % page_size``.
     For a group that keeps all keys the table is as wide as the longest sequence; for a window it
     is a ring just wide enough for the window plus the tokens of one step.
@@ -130,8 +130,9 @@ class KVGroup:
         shape = (n_layers, n_pages + 1, need.num_kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
-        self.table_host = torch.zeros((n_slots, self.table_width), dtype=torch.int32)
-        self.page_table = torch.zeros((n_slots, self.table_width), dtype=torch.int32, device=device)
+        # row n_slots stays all zero: padded rows of a batch use it and land in page 0
+        self.table_host = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32)
+        self.page_table = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32, device=device)
         self._dirty = set()
         self._mapped: Dict[int, int] = {}   # slot -> logical pages mapped so far
 

@@ -38,7 +38,7 @@ class Runner:
     """A model with its cache: opens and closes sequences and runs steps."""
 
     def __init__(self, model: DecoderModel, max_tokens: int, max_batch: int = 256,
-                 prefill_chunk: int = 2048, max_step_tokens: int = 16384):
+                 prefill_chunk: int = 2048, max_step_tokens: int = 16384, use_graphs: bool = True):
         self.model = model
         self.device = model.device
         self.prefill_chunk = max(1, prefill_chunk)
@@ -46,6 +46,7 @@ class Runner:
         self.cache = SequenceCache(model.cache_needs(), max_tokens, max_batch, model.plan.max_positions,
                                    self.prefill_chunk, model.act_dtype, self.device)
         self.vocab_size = model.plan.vocab_size
+        self.use_graphs = use_graphs
         self.steps_run = 0
         self.launch_count = 0
 

@@ -1,0 +1,89 @@
+"""Sampling settings, the reference's random generator, and the batched sampler that calls the
+device kernel.
+
+Reference: src/sampler.rs.  ``Sampler::new(temperature, top_k, top_p, seed)`` (:11-18; a zero
+seed becomes 1); greedy iff temperature <= 0 (:37-39); the generator is xorshift64* whose top 24
+bits make a float in [0, 1) (:20-30).  Defaults are the command line's: temperature 0, top-k 64,
+top-p 0.95, seed 42 (src/main.rs:182-185, src/engine.rs:341-351).
+
+Each sequence has a generator of its own, so what a sequence draws does not depend on the
+batch it is in.  The uniform numbers are drawn on the host; selection, softmax, the top-p cut
+and the walk run in the ``sampling`` CUDA unit.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import kernels
+
+_MASK = (1 << 64) - 1
+
+
+class Xorshift64Star:
+    def __init__(self, seed: int):
+        self.state = max(int(seed) & _MASK, 1)
+
+    def next_f32(self) -> float:
+        x = self.state
+        x ^= x >> 12
+        x ^= (x << 25) & _MASK
+        x ^= x >> 27
+        self.state = x
+        r = (x * 0x2545F4914F6CDD1D) & _MASK
+        return (r >> 40) / float(1 << 24)   # exact in float32
+
+
+@dataclasses.dataclass(frozen=True)
+class SamplingParams:
+    temperature: float = 0.0
+    top_k: int = 64
+    top_p: float = 0.95
+    seed: int = 42
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0
+
+    def check(self) -> None:
+        if self.greedy:
+            return
+        if not 1 <= self.top_k <= kernels.MAX_TOP_K:
+            raise ValueError(f"top_k must be between 1 and {kernels.MAX_TOP_K} when temperature > 0 "
+                             f"(got {self.top_k}); the device sampler keeps its candidates in shared memory")
+        if not 0.0 < self.top_p:
+            raise ValueError(f"top_p must be positive, got {self.top_p}")
+
+
+class BatchSampler:
+    """One generator per sequence; ``sample`` draws one token for each given sequence."""
+
+    def __init__(self, params: Sequence[SamplingParams], device):
+        for p in params:
+            p.check()
+        self.params = list(params)
+        self.rngs = [Xorshift64Star(p.seed) for p in params]
+        self.device = device
+        self.all_greedy = all(p.greedy for p in params)
+
+    def sample(self, logits: torch.Tensor, seqs: Sequence[int]) -> List[int]:
+        """``logits``: float32 [len(seqs), vocab] on the device; ``seqs``: which sequence each
+        row belongs to.  Returns one token id per row."""
+        return self.sample_device(logits, seqs).tolist()
+
+    def sample_device(self, logits: torch.Tensor, seqs: Sequence[int]) -> torch.Tensor:
+        n = len(seqs)
+        out = torch.empty(n, dtype=torch.int32, device=logits.device)
+        if self.all_greedy:
+            kernels.sample(logits, out)
+            return out
+        temps = [self.params[s].temperature for s in seqs]
+        ks = [self.params[s].top_k for s in seqs]
+        ps = [self.params[s].top_p for s in seqs]
+        us = [0.0 if self.params[s].greedy else self.rngs[s].next_f32() for s in seqs]
+        f = torch.tensor([temps, ps, us], dtype=torch.float32).pin_memory().to(logits.device, non_blocking=True)
+        k = torch.tensor(ks, dtype=torch.int32).pin_memory().to(logits.device, non_blocking=True)
+        kernels.sample(logits, out, f[0], k, f[1], f[2])
+        return out

@@ -1,0 +1,122 @@
+"""Slots, pages and per-sequence state: nothing lost, held twice or freed twice (no GPU)."""
+import random
+
+import pytest
+import torch
+
+from gemmars_b200.cache import (CacheError, KVNeed, PageAllocator, SequenceCache, SlotAllocator, StateNeed)
+
+
+def test_slots_are_reused_lowest_first():
+    s = SlotAllocator(3)
+    assert [s.take(), s.take(), s.take()] == [0, 1, 2]
+    with pytest.raises(CacheError, match="no free slot"):
+        s.take()
+    s.give_back(1)
+    with pytest.raises(CacheError, match="not held"):
+        s.give_back(1)
+    assert s.take() == 1 and s.held == {0, 1, 2}
+    with pytest.raises(CacheError):
+        s.give_back(7)
+
+
+def test_pages_never_hand_out_page_zero_and_refuse_double_free():
+    p = PageAllocator(4)
+    got = [p.take() for _ in range(4)]
+    assert sorted(got) == [1, 2, 3, 4]
+    with pytest.raises(CacheError, match="full"):
+        p.take()
+    p.give_back(3)
+    with pytest.raises(CacheError, match="not held"):
+        p.give_back(3)
+    assert p.take() == 3
+
+
+def _cache(needs, max_tokens=64 * 6, slots=4, chunk=64, max_pos=0):
+    return SequenceCache(needs, max_tokens, slots, max_pos, chunk, torch.float32, "cpu")
+
+
+def test_groups_by_need_and_layout():
+    full, win = KVNeed(2, 16), KVNeed(2, 16, window=40)
+    c = _cache([(0, win), (1, full), (2, win), (4, StateNeed((3, 5)))])
+    assert len(c.kv_groups) == 2 and len(c.state_groups) == 1
+    assert (c.bindings[0].group, c.bindings[0].index) == (0, 0) and (c.bindings[2].group, c.bindings[2].index) == (0, 1)
+    assert c.bindings[1].group == 1 and c.bindings[4].kind == "state"
+    g_win, g_full = c.kv_groups
+    assert g_full.k.shape == (1, 7, 2, 64, 16) and g_win.k.shape[0] == 2
+    assert g_full.table_width == 6 and g_win.table_width == (40 - 1 + 64 + 63) // 64 + 1 == 3
+    assert c.state(4).shape == (5, 3, 5)
+
+
+def test_extend_close_accounting_and_ring():
+    c = _cache([(0, KVNeed(1, 16)), (1, KVNeed(1, 16, window=40))])
+    full, win = c.kv_groups
+    s = c.open()
+    assert c.extend(s, 70) == 0 and c.lengths[s] == 70
+    assert full.pages.held_count == 2 and win.pages.held_count == 2
+    assert c.extend(s, 200) == 70
+    assert full.pages.held_count == 5 and win.pages.held_count == 3          # the ring stops growing
+    row = win.table_host[s].tolist()
+    assert len(set(row)) == 3 and 0 not in row
+    with pytest.raises(CacheError, match="exceeds"):
+        c.extend(s, 10_000)
+    assert not c.can_extend([(s, 200)])
+    s2 = c.open()
+    assert c.can_extend([(s2, 64)]) and not c.can_extend([(s2, 65)])
+    c.close(s)
+    assert full.pages.held_count == 0 and win.pages.held_count == 0 and full.table_host[s].sum() == 0
+    with pytest.raises(CacheError):
+        c.close(s)
+    assert c.open() == s                                                   # the slot is used again
+
+
+def test_truncate_and_state_clear():
+    c = _cache([(0, KVNeed(1, 16)), (1, StateNeed((4,)))])
+    s = c.open()
+    c.extend(s, 130)
+    c.state(1)[s] += 3.0
+    c.truncate(s, 60)
+    assert c.lengths[s] == 60 and c.kv_groups[0].pages.held_count == 1
+    assert c.extend(s, 10) == 60 and c.kv_groups[0].pages.held_count == 2
+    c.close(s)
+    s = c.open()
+    assert float(c.state(1)[s].abs().sum()) == 0.0                           # cleared when the slot is taken
+
+
+def test_max_positions_bounds_a_sequence():
+    c = _cache([(0, KVNeed(1, 16))], max_tokens=64 * 8, max_pos=100)
+    s = c.open()
+    c.extend(s, 100)
+    with pytest.raises(CacheError):
+        c.extend(s, 1)
+
+
+def test_random_walk_keeps_the_books():
+    rnd = random.Random(0)
+    c = _cache([(0, KVNeed(1, 16)), (1, KVNeed(1, 16, window=70))], max_tokens=64 * 12, slots=5)
+    full, win = c.kv_groups
+    live = {}
+    for _ in range(600):
+        op = rnd.random()
+        if op < 0.3 and c.slots.free_count:
+            live[c.open()] = 0
+        elif op < 0.8 and live:
+            s = rnd.choice(list(live))
+            n = rnd.randint(1, 90)
+            if c.can_extend([(s, n)]):
+                assert c.extend(s, n) == live[s]
+                live[s] += n
+        elif live:
+            s = rnd.choice(list(live))
+            c.close(s)
+            del live[s]
+        # books: pages held = pages the live sequences need; no page held twice
+        want_full = sum(-(-n // 64) for n in live.values())
+        assert full.pages.held_count == want_full and c.slots.held == set(live)
+        pages = [int(p) for s, n in live.items() for p in full.table_host[s, :-(-n // 64)]]
+        assert len(pages) == len(set(pages)) and 0 not in pages
+        wpages = [int(p) for s, n in live.items() for p in win.table_host[s, :min(win.table_width, -(-n // 64))]]
+        assert len(wpages) == len(set(wpages)) == win.pages.held_count and 0 not in wpages
+    for s in list(live):
+        c.close(s)
+    assert full.pages.held_count == 0 and win.pages.held_count == 0 and c.slots.free_count == 5

@@ -1,0 +1,124 @@
+"""The generation loop's decisions, with a fake model (no GPU)."""
+import pytest
+
+from gemmars_b200.cache import CacheError, SlotAllocator
+from gemmars_b200.engine.generate import CANCELLED, LENGTH, STOP, GenerationLoop, Request, plan_batches, tokens_held
+
+
+class FakeModel:
+    """Next token = (sum of the sequence so far) % 50; records every call."""
+
+    def __init__(self, n_slots):
+        self.slots = SlotAllocator(n_slots)
+        self.seqs, self.calls, self.opened = {}, [], []
+
+    def open(self):
+        s = self.slots.take()
+        self.seqs[s] = []
+        self.opened.append(s)
+        return s
+
+    def close(self, s):
+        self.slots.give_back(s)
+        del self.seqs[s]
+
+    def step(self, items):
+        self.calls.append([(s, list(t)) for s, t in items])
+        rows = []
+        for s, toks in items:
+            self.seqs[s].extend(toks)
+            rows.append(sum(self.seqs[s]) % 50)
+        return rows
+
+    class Sampler:
+        def __init__(self, params):
+            self.params = params
+
+        def sample(self, logits, seqs):
+            assert len(logits) == len(seqs)
+            return list(logits)
+
+    def loop(self, max_batch=4, pages=100, max_context=None):
+        return GenerationLoop(self.open, self.close, self.step, self.Sampler, max_batch, pages, 64, max_context)
+
+
+def _expected(prompt, n, stop=()):
+    seq, out = list(prompt), []
+    for _ in range(n):
+        t = sum(seq) % 50
+        out.append(t)
+        if t in stop:
+            return out, STOP
+        seq.append(t)
+    return out, LENGTH
+
+
+def test_unequal_prompts_end_at_different_times_and_free_their_slots():
+    m = FakeModel(4)
+    reqs = [Request([1, 2, 3], 6), Request([9], 2), Request([4, 4, 4, 4, 4], 4), Request([7, 1], 1)]
+    res = m.loop().run(reqs)
+    for r, q in zip(res, reqs):
+        assert (r.tokens, r.reason) == _expected(q.prompt, q.max_tokens) and r.prompt_tokens == len(q.prompt)
+    # one step for all prompts, then one token per live sequence; sequences leave the batch when they end
+    assert [len(c) for c in m.calls] == [4, 3, 2, 2, 1, 1]
+    assert all(len(t) == 1 for c in m.calls[1:] for _, t in c)
+    assert m.slots.free_count == 4 and not m.seqs
+    assert [r.forwards for r in res] == [5, 1, 3, 0]      # the last generated token is never run
+
+
+def test_stop_token_is_kept_and_not_run():
+    m = FakeModel(2)
+    prompt = [10, 5]                       # 15 -> 30 -> 10 -> ...
+    res = m.loop().run([Request(prompt, 10, stop_ids=(10,))])
+    assert res[0].tokens == [15, 30, 10] and res[0].reason == STOP
+    assert m.calls[-1] == [(0, [30])]      # the stop token 10 never ran
+
+
+def test_batches_follow_one_another_and_reuse_slots():
+    m = FakeModel(2)
+    reqs = [Request([i + 1], 3) for i in range(5)]
+    res = m.loop(max_batch=2).run(reqs)
+    assert [r.tokens for r in res] == [_expected(q.prompt, 3)[0] for q in reqs]
+    assert m.opened == [0, 1, 0, 1, 0]
+    assert plan_batches(reqs, 2, 100, 64) == [[0, 1], [2, 3], [4]]
+
+
+def test_batches_respect_the_cache():
+    reqs = [Request([1] * 100, 30), Request([1] * 10, 10), Request([1] * 200, 57), Request([1], 1)]
+    assert tokens_held(100, 30, None) == 129 and tokens_held(100, 30, 110) == 110
+    assert plan_batches(reqs, 8, 6, 64) == [[0, 1], [2, 3]]          # 3 + 1 pages, then 4 + 1
+    with pytest.raises(ValueError, match="cache pages"):
+        plan_batches(reqs, 8, 3, 64)
+    with pytest.raises(ValueError, match="empty prompt"):
+        plan_batches([Request([], 3)], 8, 6, 64)
+    with pytest.raises(ValueError, match="context limit"):
+        plan_batches(reqs, 8, 60, 64, max_context=150)
+
+
+def test_cancel_and_context_limit_and_zero_tokens():
+    m = FakeModel(3)
+    seen = []
+
+    def on_token(i, toks):
+        seen.append((i, list(toks)))
+        return not (i == 0 and len(toks) == 2)
+
+    reqs = [Request([1, 2], 5), Request([3], 5), Request([4], 0)]
+    res = m.loop(max_context=3).run(reqs, on_token)
+    assert res[0].reason == CANCELLED and len(res[0].tokens) == 2
+    # request 1: prompt of 1, context 3 -> runs tokens until 3 positions are held, then "length"
+    assert res[1].reason == LENGTH and len(res[1].tokens) == 3 and res[1].forwards == 2
+    assert res[2].tokens == [] and res[2].reason == LENGTH
+    assert (0, res[0].tokens) in seen and m.slots.free_count == 3
+
+
+def test_slots_are_given_back_when_a_step_fails():
+    m = FakeModel(2)
+
+    def bad_step(items):
+        raise CacheError("boom")
+
+    loop = GenerationLoop(m.open, m.close, bad_step, m.Sampler, 2, 100, 64)
+    with pytest.raises(CacheError):
+        loop.run([Request([1], 2), Request([2], 2)])
+    assert m.slots.free_count == 2
