@@ -1,0 +1,151 @@
+"""Generation through the Python entry point and the command line, and the device sampler."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from tiny_configs import TINY_A, TINY_B
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _prompts(cfg, lengths, seed=0):
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lengths]
+
+
+@pytest.mark.parametrize("cfg", [TINY_A, TINY_B], ids=["A", "B"])
+def test_greedy_generation_matches_plain(cfg, model_folders):
+    from gemmars_b200 import Engine
+    folder = model_folders(cfg)
+    pcfg, w = plain.load_folder(folder)
+    eng = Engine.load(folder, "dtype=float32;max_batch=3;max_tokens=2048")
+    prompts = _prompts(cfg, [7, 13, 1, 40, 66])
+    # a stop token that greedy decoding really meets: the 5th token the plain model generates for prompt 0
+    free_run, _ = plain.generate(pcfg, w, prompts[0], 12)
+    stop = [free_run[4]]
+    res = eng.generate(prompts, max_tokens=12, stop_ids=stop)
+    for p, r in zip(prompts, res):
+        want, reason = plain.generate(pcfg, w, p, 12, stop=stop)
+        assert r.tokens == want and r.reason == reason
+    assert res[0].reason == "stop" and len(res[0].tokens) <= 5
+    assert eng.runner.cache.pages_held() == 0 and eng.runner.cache.slots.free_count == eng.runner.cache.n_slots
+    # the same requests in another batch composition give the same tokens
+    again = eng.generate(list(reversed(prompts)), max_tokens=12, stop_ids=stop)
+    assert [r.tokens for r in reversed(again)] == [r.tokens for r in res]
+
+
+def test_bfloat16_generation_runs_and_mostly_agrees(model_folders):
+    from gemmars_b200 import Engine
+    folder = model_folders(TINY_A)
+    pcfg, w = plain.load_folder(folder)
+    eng = Engine.load(folder, "dtype=bfloat16;max_batch=4")
+    prompts = _prompts(TINY_A, [9, 3, 30, 17], seed=3)
+    res = eng.generate(prompts, max_tokens=8, stop_ids=[])
+    # greedy tokens can differ from the float64 oracle only where two logits are nearly tied
+    for p, r in zip(prompts, res):
+        seq = list(p)
+        for tok in r.tokens:
+            logits = plain.forward(pcfg, w, seq)[-1]
+            assert logits.max() - logits[tok] <= 2e-2 * np.abs(logits).max()
+            seq.append(tok)
+
+
+def test_conversation_keeps_its_cache(model_folders):
+    from gemmars_b200 import Engine
+    folder = model_folders(TINY_B)
+    pcfg, w = plain.load_folder(folder)
+    eng = Engine.load(folder, "dtype=float32")
+    eng.set("max_tokens", 5)
+    eng.set("stop", "")
+    first = [5, 9, 200, 31]
+    r1 = eng.send(first)
+    want1, _ = plain.generate(pcfg, w, first, 5)
+    assert r1.tokens == want1 and r1.reason == "length"
+    # the second turn continues from the cache; the last generated token was not run and is fed first
+    second = [77, 12]
+    r2 = eng.send(second)
+    want2, _ = plain.generate(pcfg, w, first + want1 + second, 5)
+    assert r2.tokens == want2
+    eng.reset()
+    assert eng.send(first).tokens == want1
+
+
+def test_device_sampler_matches_the_plain_sampler():
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(5)
+    vocab = 3001
+    logits = (rng.standard_normal((6, vocab)) * 3).astype(np.float32)
+    logits[1, 100] = logits[1, 2000] = logits[1].max() + 1.0        # a tie at the top: lower id wins
+    logits[4, :50] = 2.5                                               # many ties around the k-th place
+    params = [(0.0, 64, 0.95), (0.0, 64, 0.95), (0.7, 64, 0.95), (1.3, 1, 1.0), (1.0, 20, 0.5), (0.9, 1024, 1.0)]
+    dev = torch.from_numpy(logits).cuda()
+    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    for trial in range(20):
+        samplers = [plain.Sampler(t, k, p, seed=trial * 7 + i + 1) for i, (t, k, p) in enumerate(params)]
+        us = []
+        for s in samplers:
+            state = s.rng
+            us.append(float(s.next_f32()) if s.temperature > 0 else 0.0)
+            s.rng = state
+        kernels.sample(dev, out,
+                       torch.tensor([p[0] for p in params], dtype=torch.float32, device="cuda"),
+                       torch.tensor([p[1] for p in params], dtype=torch.int32, device="cuda"),
+                       torch.tensor([p[2] for p in params], dtype=torch.float32, device="cuda"),
+                       torch.tensor(us, dtype=torch.float32, device="cuda"))
+        got = out.tolist()
+        want = [s.sample(logits[i]) for i, s in enumerate(samplers)]
+        assert got == want, f"trial {trial}: {got} != {want}"
+    kernels.sample(dev, out)                                           # all greedy
+    assert out.tolist() == [plain.argmax(r) for r in logits]
+
+
+def test_temperature_sampling_is_seeded(model_folders):
+    from gemmars_b200 import Engine, SamplingParams
+    folder = model_folders(TINY_A)
+    eng = Engine.load(folder, "dtype=float32;max_batch=2")
+    prompts = _prompts(TINY_A, [5, 11, 8], seed=9)
+    sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.9, seed=123)
+    a = eng.generate(prompts, max_tokens=10, sampling=sp, stop_ids=[])
+    b = eng.generate(prompts, max_tokens=10, sampling=sp, stop_ids=[])
+    c = eng.generate(prompts, max_tokens=10, sampling=SamplingParams(0.8, 50, 0.9, seed=124), stop_ids=[])
+    assert [r.tokens for r in a] == [r.tokens for r in b] != [r.tokens for r in c]
+    # against the plain model and sampler, sequence i seeded seed + i
+    pcfg, w = plain.load_folder(folder)
+    for i, (p, r) in enumerate(zip(prompts, a)):
+        want, _ = plain.generate(pcfg, w, p, 10, temperature=0.8, top_k=50, top_p=0.9, seed=123 + i)
+        assert r.tokens == want
+    with pytest.raises(ValueError, match="top_k"):
+        eng.generate(prompts, sampling=SamplingParams(temperature=1.0, top_k=0))
+
+
+def test_command_line(model_folders, tmp_path):
+    folder = model_folders(TINY_A)
+    pcfg, w = plain.load_folder(folder)
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    base = [sys.executable, "-m", "gemmars_b200", "--model", folder, "--dtype", "float32"]
+    p = subprocess.run(base + ["--tokens", ",".join(map(str, prompt)), "-n", "6"], capture_output=True, text=True,
+                       cwd=ROOT, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    want, _ = plain.generate(pcfg, w, prompt, 6, stop=[7])
+    assert [int(x) for x in p.stdout.strip().split(",")] == want
+    assert "tok/s" in p.stderr
+    dump = tmp_path / "logits.bin"
+    p = subprocess.run(base + ["--tokens", ",".join(map(str, prompt)), "--dump-logits", str(dump)],
+                       capture_output=True, text=True, cwd=ROOT, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    got = np.fromfile(dump, dtype="<f4")
+    assert np.abs(got - plain.forward(pcfg, w, prompt)[-1]).max() < 2e-5
+    batch = tmp_path / "batch.txt"
+    batch.write_text("1 2 3\n9,8,7,6,5\n")
+    p = subprocess.run(base + ["--batch-file", str(batch), "-n", "4"], capture_output=True, text=True, cwd=ROOT,
+                       timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    rows = [json.loads(l) for l in p.stdout.splitlines()]
+    assert rows[1]["tokens"] == plain.generate(pcfg, w, [9, 8, 7, 6, 5], 4, stop=[7])[0]
