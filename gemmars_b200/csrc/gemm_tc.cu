@@ -1,0 +1,417 @@
+// bfloat16 matrix product on the 5th-generation tensor cores (tcgen05, sm_100a):
+//
+//     y[t, o] = sum_i W[o, i] * x[t, i] (+ bias[o])          (src/kernels.rs:54-57)
+//
+// written in bfloat16 or float32, or added into a float32 y (the residual stream).
+//
+// The product is computed "swapped": a CTA owns 128 output features (rows of W, the MMA's M) by
+// BN tokens (rows of x, the MMA's N, 16..256).  Both operands are K-major in memory as they
+// are, so TMA brings [128 x 64] tiles of W and [BN x 64] tiles of x into 128-byte-swizzled
+// shared memory, one elected thread issues tcgen05.mma with the accumulator in tensor memory
+// (lane = feature, column = token), and four warps read it back with tcgen05.ld: for one
+// token, the 32 lanes of a warp hold 32 consecutive features, so stores are coalesced.
+//
+// One kernel serves prompts (BN = 256, 128 or 64) and decoding (BN = 16..64, where the CTA
+// only streams its rows of W at memory speed).  When decoding leaves too few tiles for the
+// 148 SMs, the inner dimension is split over the CTAs of a thread-block cluster, whose partial
+// sums are added in rank order through distributed shared memory: no atomics, the same bits
+// every run.
+//
+// Warp roles (192 threads): warps 0-3 epilogue (tensor-memory lane quarter = warp id),
+// warp 4 TMA producer, warp 5 tensor-memory allocation and MMA issue.
+//
+// Every wait on an mbarrier is bounded: after WAIT_LIMIT polls the thread records a code in
+// the status word and goes on to the common exit, where tensor memory is freed.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;          // output features per CTA (MMA M)
+constexpr int BK = 64;           // inner elements per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2 };
+enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
+
+__device__ int g_status;   // first failure of any launch; 0 when all waits completed
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when the limit ran out (the caller records it and leaves its loop).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+        "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t cluster_size() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
+  uint32_t addr;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  return (uint64_t)((addr & 0x3ffff) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+
+template <int MODE>
+__device__ __forceinline__ void emit(void* y, size_t idx, float v) {
+  if (MODE == EPI_STORE_BF16) ((bf16*)y)[idx] = __float2bfloat16_rn(v);
+  else if (MODE == EPI_STORE_F32) ((float*)y)[idx] = v;
+  else ((float*)y)[idx] += v;
+}
+
+// ------------------------------------------------------------------ the kernel
+// grid = (token tiles, feature tiles, K splits); a cluster spans the K splits of one tile.
+template <int BN, int STAGES, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy) {
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_bar = empty_bar + STAGES;
+  uint32_t* tmem_slot = (uint32_t*)(tmem_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BN, n0 = blockIdx.y * BM;
+  const uint32_t nsplit = cluster_size(), split = cluster_rank();
+  const int kb_total = (K + BK - 1) / BK;
+  const int kb_begin = (int)((long long)kb_total * split / nsplit), kb_end = (int)((long long)kb_total * (split + 1) / nsplit);
+  const int kb_count = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      for (int i = 0; i < kb_count; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
+          atomicCAS(&g_status, ST_OK, ST_TIMEOUT_EMPTY);
+          break;
+        }
+        uint8_t* a = smem + s * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
+        tma_load_2d(a + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ---------------- MMA issue
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < kb_count && ok; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
+          atomicCAS(&g_status, ST_OK, ST_TIMEOUT_FULL);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along the swizzled row per step
+          tc_mma(tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+      }
+      tc_commit(tmem_bar);         // the accumulator is complete once everything issued has run
+    }
+    __syncwarp();
+  }
+
+  // ---------------- epilogue (warps 0-3); the other warps wait at the barriers below
+  float* partial = (float*)smem;   // [BN][BM] float32, over the pipeline stages (idle by then)
+  bool have_acc = false;
+  if (warp < 4) {
+    if (kb_count > 0) {
+      have_acc = __all_sync(0xffffffffu, mbar_wait(tmem_bar, 0));   // the same answer in every lane
+      if (!have_acc && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
+    }
+    tc_fence_after();
+  }
+  if (nsplit > 1) {
+    // every rank publishes its partial sums; rank 0 adds them in rank order
+    if (warp < 4) {
+      const int f = warp * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        uint32_t v[16];
+        if (have_acc) {
+          tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+          tc_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) partial[(c + j) * BM + f] = __uint_as_float(v[j]);
+      }
+    }
+    cluster_sync();
+    if (split == 0 && warp < 4) {
+      const int f = warp * 32 + lane, n = n0 + f;
+      const float b = (bias && n < N) ? bias[n] : 0.f;
+      for (int c = 0; c < BN; ++c) {
+        const int m = m0 + c;
+        if (m >= M) break;
+        float acc = partial[c * BM + f];
+        for (uint32_t r = 1; r < nsplit; ++r) acc += ld_peer_f32(&partial[c * BM + f], r);
+        if (n < N) emit<MODE>(y, (size_t)m * ldy + n, acc + b);
+      }
+    }
+    cluster_sync();  // peers keep their shared memory until rank 0 has read it
+  } else if (warp < 4 && have_acc) {
+    const int f = warp * 32 + lane, n = n0 + f;
+    const float b = (bias && n < N) ? bias[n] : 0.f;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+      if (m0 + c >= M) break;
+      uint32_t v[16];
+      tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+      tc_wait_ld();
+      if (n < N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c + j;
+          if (m < M) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + b);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+  static EncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiled)p;
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, pitch;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.base;
+    for (uint64_t v : {k.rows, k.cols, k.pitch, (uint64_t)k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    return h;
+  }
+};
+
+// A [rows, cols] bfloat16 matrix with rows `pitch` bytes apart, cut into [box_rows, 64] boxes.
+// Maps are remembered: weights and reused activation buffers are encoded once.
+bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex mu;
+  MapKey key{base, rows, cols, pitch, box_rows};
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return true;
+  }
+  EncodeTiled fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {BK, box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 65536) cache.clear();
+  cache.emplace(key, *out);
+  return true;
+}
+
+template <int BN, int STAGES, int MODE>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K, long long ldy,
+           int splits, cudaStream_t stream) {
+  constexpr size_t SMEM = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
+  static_assert((size_t)BN * BM * 4 <= (size_t)STAGES * (BM * BK * 2 + BN * BK * 2), "partial sums need the stage memory");
+  auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+      return (int)cudaGetLastError();
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((M + BN - 1) / BN, (N + BM - 1) / BM, splits);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = splits;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, bias, y, M, N, K, ldy);
+}
+
+template <int BN, int STAGES>
+int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K,
+                long long ldy, int splits, cudaStream_t stream) {
+  switch (mode) {
+    case EPI_STORE_BF16: return launch<BN, STAGES, EPI_STORE_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case EPI_STORE_F32: return launch<BN, STAGES, EPI_STORE_F32>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case EPI_ACCUMULATE_F32: return launch<BN, STAGES, EPI_ACCUMULATE_F32>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+  }
+  return GB_ERR_ARG;
+}
+
+}  // namespace
+
+// x: [M, K] bfloat16, rows ldx elements apart; w: [N, K] bfloat16 contiguous; y: [M, N], rows ldy apart.
+// mode: 0 store bfloat16, 1 store float32, 2 add into float32.  bn: tokens per tile (16, 32, 64, 128, 256);
+// splits: CTAs of a cluster sharing the inner dimension (1, 2, 4, 8; only with bn <= 64).
+// Needs K % 8 == 0, ldx % 8 == 0 and 16-byte aligned x and w (TMA rules).
+GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N, int K,
+                         long long ldx, long long ldy, int bn, int splits, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return GB_ERR_SIZE;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return GB_ERR_ARG;
+  if (splits > 1 && bn > 64) return GB_ERR_ARG;
+  CUtensorMap mw, mx;
+  if (!tensor_map(&mw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
+  if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  switch (bn) {
+    case 16: return launch_mode<16, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case 32: return launch_mode<32, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case 64: return launch_mode<64, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case 128: return launch_mode<128, 6>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case 256: return launch_mode<256, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+  }
+  return GB_ERR_SIZE;
+}
+
+// The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator).
+// Synchronizes the device; for tests and health checks, not for the step.
+GB_EXPORT int gb_gemm_tc_status(int reset) {
+  int v = -1;
+  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+  if (reset) {
+    int zero = 0;
+    cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+  }
+  return v;
+}

@@ -185,11 +185,9 @@ class Engine:
                         tuple(self.stop_ids if stop_ids is None else stop_ids),
                         dataclasses.replace(base, seed=base.seed + i)) for i, p in enumerate(prompts)]
         loop = self._loop()
-        t0 = time.perf_counter()
         results = loop.run(reqs, on_token)
-        torch.cuda.synchronize(self.runner.device)
-        dt = time.perf_counter() - t0
-        self.stats = Stats(sum(len(p) for p in prompts), sum(len(r.tokens) for r in results), 0.0, dt, loop.decode_steps)
+        self.stats = Stats(sum(len(p) for p in prompts), loop.decode_tokens, loop.prefill_secs, loop.decode_secs,
+                           loop.decode_steps)
         return results
 
     def complete(self, prompt: Sequence[int], on_token=None) -> Generated:
@@ -201,11 +199,9 @@ class Engine:
         return self._timed(loop, [req], cb)[0]
 
     def _timed(self, loop, reqs, cb):
-        t0 = time.perf_counter()
         res = loop.run(reqs, cb)
-        torch.cuda.synchronize(self.runner.device)
-        self.stats = Stats(sum(len(r.prompt) for r in reqs), sum(len(r.tokens) for r in res), 0.0,
-                           time.perf_counter() - t0, loop.decode_steps)
+        self.stats = Stats(sum(len(r.prompt) for r in reqs), loop.decode_tokens, loop.prefill_secs,
+                           loop.decode_secs, loop.decode_steps)
         return res
 
     def send(self, tokens: Sequence[int], on_token=None) -> Generated:

@@ -17,6 +17,7 @@ current logits, push, stop check (the stop token is not run), callback, forward 
 from __future__ import annotations
 
 import dataclasses
+import time
 from typing import Callable, List, Optional, Sequence
 
 STOP, LENGTH, CANCELLED = "stop", "length", "cancelled"
@@ -79,6 +80,11 @@ class GenerationLoop:
         self.max_batch, self.cache_pages, self.page_size, self.max_context = max_batch, cache_pages, page_size, max_context
         self.decode_steps = 0
         self.prefill_steps = 0
+        # wall time up to the first sampled tokens of each batch, and after (sampling reads the
+        # tokens back to the host, so both include the device work they wait for)
+        self.prefill_secs = 0.0
+        self.decode_secs = 0.0
+        self.decode_tokens = 0
 
     def run(self, requests: Sequence[Request],
             on_token: Optional[Callable[[int, List[int]], bool]] = None) -> List[Generated]:
@@ -104,11 +110,19 @@ class GenerationLoop:
             for i in list(live):
                 if requests[i].max_tokens <= 0:
                     self._finish(i, LENGTH, requests, out, forwards, results, slots, live)
+            t_mark, first = time.perf_counter(), True
             if live:
                 logits = self.step([(slots[i], list(requests[i].prompt)) for i in live])
                 self.prefill_steps += 1
             while live:
                 toks = sampler.sample(logits, [batch.index(i) for i in live])
+                now = time.perf_counter()
+                if first:
+                    self.prefill_secs += now - t_mark
+                else:
+                    self.decode_secs += now - t_mark
+                    self.decode_tokens += len(toks)
+                t_mark, first = now, False
                 nxt = []
                 for i, tok in zip(list(live), toks):
                     r = requests[i]

@@ -146,6 +146,69 @@ def gemm_ref(x, w, out, bias=None, accumulate=False):
              OUT_ACCUMULATE if accumulate else OUT_STORE, m, n, k, x.stride(0), out.stride(0), _stream()), "gemm_ref")
 
 
+_SM_COUNT = 148
+_TC_MODES = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2}
+
+
+def gemm_tc_usable(x, w) -> bool:
+    """Whether the tensor-core kernel takes these operands (TMA wants 16-byte aligned rows)."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_tiling(m: int, n: int, k: int):
+    """(tokens per tile, K splits) for an [m, k] x [n, k]^T product."""
+    tiles_n = -(-n // 128)
+    if m <= 64:
+        bn = 16 if m <= 16 else (32 if m <= 32 else 64)
+        tiles, kb = tiles_n, -(-k // 64)
+        splits = 1
+        # too few tiles to keep every SM streaming: split the inner dimension over a cluster
+        while splits < 8 and tiles * splits < 120 and kb // (splits * 2) >= 4:
+            splits *= 2
+        return bn, splits
+    best, best_score = 128, -1.0
+    for bn, tile_eff in ((256, 1.0), (128, 0.92)):
+        tiles = tiles_n * -(-m // bn)
+        waves = -(-tiles // _SM_COUNT)
+        fill = m / (-(-m // bn) * bn)
+        score = tile_eff * fill * tiles / (waves * _SM_COUNT)
+        if score > best_score:
+            best, best_score = bn, score
+    return best, 1
+
+
+def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None):
+    """out = x @ w.T (+ bias) (bfloat16 or float32 out) or out += ... (float32 out), bfloat16
+    operands, on the tcgen05 tensor cores."""
+    _cuda(x, w, out, bias)
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and w.is_contiguous() and out.shape == (m, n) and out.stride(1) == 1
+    if not gemm_tc_usable(x, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows (K and the row stride "
+                          "multiples of 8)")
+    mode = _TC_MODES.get((out.dtype, bool(accumulate)))
+    if mode is None:
+        raise KernelError(f"gemm_tc: cannot {'add into' if accumulate else 'store'} {out.dtype}")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+    auto_bn, auto_splits = gemm_tc_tiling(m, n, k)
+    f = _fn("gemm_tc", "gb_gemm_tc",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+             c_int, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
+             bn or auto_bn, splits or auto_splits, _stream()), "gemm_tc")
+
+
+def gemm_tc_status(reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in a gemm_tc launch (synchronizes)."""
+    lib = build.load("gemm_tc")
+    lib.gb_gemm_tc_status.argtypes = [c_int]
+    lib.gb_gemm_tc_status.restype = c_int
+    return lib.gb_gemm_tc_status(1 if reset else 0)
+
+
 # --------------------------------------------------------------------------- attention
 
 def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None):
@@ -178,13 +241,18 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None):
 
 def gemm_units(compute: str):
     """The units ``gemm`` may launch for a model computed in ``compute``."""
-    return [("gemm_ref", ())]
+    return [("gemm_ref", ())] if compute == "float32" else [("gemm_tc", ()), ("gemm_ref", ())]
 
 
 def gemm(x, w, out, bias=None, accumulate=False):
     """out = x @ w.T (+ bias) or, with ``accumulate``, out += ...; picks the kernel for the
-    precision and the number of rows."""
-    gemm_ref(x, w, out, bias, accumulate)
+    precision and the shape: float32 runs on the CUDA cores in a fixed order; bfloat16 runs on the
+    tensor cores, except for operands whose rows TMA cannot address (an inner size that is not
+    a multiple of 8), which the plain kernel takes."""
+    if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w):
+        gemm_tc(x, w, out, bias, accumulate)
+    else:
+        gemm_ref(x, w, out, bias, accumulate)
 
 
 def attention_units(compute: str, head_dim: int):
