@@ -42,8 +42,21 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far (launches replayed from CUDA graphs included)."""
+    return _launches[0]
+
+
+def count_launches(n: int) -> None:
+    _launches[0] += n
+
+
 def _check(code: int, what: str):
     if code == 0:
+        _launches[0] += 1
         return
     if code < 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, 'refused')} (code {code})")
@@ -253,6 +266,11 @@ def gemm(x, w, out, bias=None, accumulate=False):
         gemm_tc(x, w, out, bias, accumulate)
     else:
         gemm_ref(x, w, out, bias, accumulate)
+
+
+def extra_units():
+    """Units no model asks for by itself (built with the rest by the build check)."""
+    return []
 
 
 def attention_units(compute: str, head_dim: int):
