@@ -110,7 +110,9 @@ class StateNeed:
 class KVGroup:
     """Storage of the layers that share one ``KVNeed``.
 
-    ``k`` and ``v``: ``[layers, pages + 1, kv_heads, page_size, head_dim]``.
+    ``k``: ``[layers, pages + 1, kv_heads, page_size, head_dim]``; ``v`` is kept transposed inside
+    a page, ``[layers, pages + 1, kv_heads, head_dim, page_size]``, so that attention's second
+    product also contracts over the contiguous axis.
     ``page_table``: ``[slots + 1, table_width]`` int32; position ``p`` of the sequence in slot ``s``
     lives in page ``page_table[s, (p // page_size) % table_width]`` at offset ``p % page_size``.
     For a group that keeps all keys the table is as wide as the longest sequence; for a window it
@@ -129,7 +131,7 @@ class KVGroup:
         self.pages = PageAllocator(n_pages)
         shape = (n_layers, n_pages + 1, need.num_kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape[:3] + (need.head_dim, page_size), dtype=dtype, device=device)
         # row n_slots stays all zero: padded rows of a batch use it and land in page 0
         self.table_host = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32)
         self.page_table = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32, device=device)
@@ -183,7 +185,8 @@ class KVGroup:
             self.page_table[idx.to(self.page_table.device)] = self.table_host[idx].to(self.page_table.device)
 
     def layer(self, i: int):
-        """(k, v) storage of the group's ``i``-th layer: ``[pages + 1, kv_heads, page_size, head_dim]``."""
+        """(k, v) storage of the group's ``i``-th layer: k ``[pages + 1, kv_heads, page_size, head_dim]``,
+        v ``[pages + 1, kv_heads, head_dim, page_size]``."""
         return self.k[i], self.v[i]
 
 

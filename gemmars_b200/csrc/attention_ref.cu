@@ -36,9 +36,8 @@ __global__ void __launch_bounds__(CHUNK) attention_ref_kernel(
     const int j = c0 + tid;
     float s = -INFINITY;
     if (j < hi) {
-      const size_t r = kv.row(slot, j, g);
-      rows[tid] = r;
-      const T* kr = kcache + r;
+      const T* kr = kcache + kv.row(slot, j, g);
+      rows[tid] = kv.vcol(slot, j, g);
       float d = 0.f;
       for (int i = 0; i < hd; ++i) d = fmaf(qs[i], to_f32(kr[i]), d);
       s = d;
@@ -55,7 +54,7 @@ __global__ void __launch_bounds__(CHUNK) attention_ref_kernel(
       const int d = tid + u * CHUNK;
       if (d < hd) {
         float a = acc[u] * alpha;
-        for (int jj = 0; jj < n; ++jj) a = fmaf(p[jj], to_f32(vcache[rows[jj] + d]), a);
+        for (int jj = 0; jj < n; ++jj) a = fmaf(p[jj], to_f32(vcache[rows[jj] + (size_t)d * kv.page_size]), a);
         acc[u] = a;
       }
     }

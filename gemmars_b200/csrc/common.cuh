@@ -67,7 +67,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   return scratch[32];
 }
 
-// The page of the cache that holds position `pos` of the sequence in `slot`, and the row in it.
+// The paged cache.  Keys: [pages, kv_heads, page_size, head_dim] (a key's dims contiguous).
+// Values are kept transposed inside a page: [pages, kv_heads, head_dim, page_size] (a dim's
+// positions contiguous), so that both products of attention contract over the contiguous axis.
 // page_table: [slots, table_width]; a ring when the sequence is longer than the table is wide.
 struct PagedKV {
   const int* page_table;
@@ -79,6 +81,12 @@ struct PagedKV {
     const int lp = pos / page_size;
     const int page = page_table[(size_t)slot * table_width + lp % table_width];
     return (((size_t)page * num_kv_heads + kv_head) * page_size + pos % page_size) * head_dim;
+  }
+  // Index of dim 0 of the value at `pos`; dim d is d * page_size further.
+  __device__ __forceinline__ size_t vcol(int slot, int pos, int kv_head) const {
+    const int lp = pos / page_size;
+    const int page = page_table[(size_t)slot * table_width + lp % table_width];
+    return ((size_t)page * num_kv_heads + kv_head) * page_size * head_dim + pos % page_size;
   }
 };
 

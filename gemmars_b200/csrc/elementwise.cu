@@ -69,7 +69,7 @@ GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtyp
 //            the token's position, then * q_scale; written back in place.
 //   k heads: optional RMSNorm (weight kw), optional rotation; written back in place and, with
 //            FLAG_CACHE, into the paged key cache.
-//   v heads: with FLAG_CACHE copied into the paged value cache.
+//   v heads: with FLAG_CACHE copied into the paged value cache (transposed inside the page).
 enum { FLAG_NORM = 1, FLAG_ROPE = 2, FLAG_CACHE = 4, FLAG_INPLACE = 8 };
 
 template <typename T>
@@ -89,8 +89,8 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
   const bool cache = flags & FLAG_CACHE;
   if (h >= nh + nkv) {  // value head
     if (!cache) return;
-    T* dst = vcache + kv.row(seq_slot[tok_seq[t]], pos, h - nh - nkv);
-    for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+    T* dst = vcache + kv.vcol(seq_slot[tok_seq[t]], pos, h - nh - nkv);
+    for (int i = lane; i < hd; i += 32) dst[(size_t)i * kv.page_size] = src[i];
     return;
   }
   const bool is_q = h < nh;

@@ -237,6 +237,42 @@ def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, to
              tok_seq.data_ptr(), seq_slot.data_ptr(), q.shape[0], nh, window or 0, _stream()), "attention_ref")
 
 
+def decode_shares(ntok: int, nh: int, nkv: int, longest: int) -> int:
+    """CTAs along the keys per (token, kv head) for the decode attention kernel: enough CTAs to
+    fill the GPU a few times over, while every warp still gets a couple of 32-key blocks."""
+    rep = nh // nkv
+    chunks = -(-rep // 16)
+    base = max(1, ntok * nkv * chunks)
+    blocks = -(-max(longest, 1) // 32)
+    want = -(-4 * _SM_COUNT // base)
+    return max(1, min(want, blocks // 16, 64))
+
+
+def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None,
+                     shares=1, scratch=None):
+    """bfloat16 attention of single positions (one CTA per token, kv head and share of the keys)
+    over the paged cache; the unit is compiled for the cache's head size."""
+    _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot, scratch)
+    nkv, hd = kcache.shape[1], kcache.shape[3]
+    ntok = q.shape[0]
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and vcache.shape[2:] == (hd, page_size)
+    if shares > 1:
+        need = ntok * nh * shares * (hd + 2)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+        assert scratch.dtype == torch.float32 and scratch.numel() >= need
+    f = _fn("attention_decode", "gb_attention_decode",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+            defines=(("GB_HEAD_DIM", hd),))
+    _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+             page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(), tok_seq.data_ptr(),
+             seq_slot.data_ptr(), ntok, nh, window or 0, shares, _ptr(scratch), _stream()), "attention_decode")
+    if shares > 1:
+        count_launches(1)   # the merge kernel
+
+
 # --------------------------------------------------------------------------- sampling
 
 def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None):
@@ -274,10 +310,23 @@ def extra_units():
 
 
 def attention_units(compute: str, head_dim: int):
-    return [("attention_ref", ())]
+    if compute == "float32":
+        return [("attention_ref", ())]
+    return [("attention_ref", ()), ("attention_decode", (("GB_HEAD_DIM", head_dim),))]
 
 
 def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=None):
     """Attention of the step's queries over the cache; picks the kernel for the precision and
-    for prompts or single tokens."""
+    for prompts or single tokens.  float32 always takes the plain kernel, whose arithmetic for a
+    position does not depend on the batch."""
+    if q.dtype == torch.bfloat16 and ctx.max_new <= DECODE_KERNEL_MAX_NEW:
+        nkv = kcache.shape[1]
+        shares = decode_shares(ctx.n_tokens, nh, nkv, ctx.max_total if window is None else min(ctx.max_total, window))
+        attention_decode(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
+                         window, shares)
+        return
     attention_ref(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, window)
+
+
+# a step whose sequences bring at most this many tokens each runs the per-position decode kernel
+DECODE_KERNEL_MAX_NEW = 1

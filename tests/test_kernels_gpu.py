@@ -1,0 +1,223 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 statement of the same operation, at
+sizes other than the engine's."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def k():
+    from gemmars_b200 import kernels
+    return kernels
+
+
+def _paged(nseq, lengths, nkv, hd, dtype, page=64, extra_pages=3, seed=0, ring=None):
+    """A paged cache filled with random keys and values for sequences of the given lengths, with a
+    shuffled page assignment; returns tensors and per-sequence dense [len, nkv, hd] copies."""
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    width = max(-(-max(lengths) // page), 1) if ring is None else ring
+    n_pages = sum(min(-(-n // page), width) for n in lengths) + extra_pages
+    kc = torch.randn((n_pages + 1, nkv, page, hd), generator=g, device="cuda").to(dtype)
+    vc = torch.randn((n_pages + 1, nkv, hd, page), generator=g, device="cuda").to(dtype)
+    perm = (torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)) + 1).tolist()
+    table = torch.zeros((nseq + 1, width), dtype=torch.int32)
+    dense = []
+    for s, n in enumerate(lengths):
+        for lp in range(min(-(-n // page), width)):
+            table[s, lp] = perm.pop()
+        ks = torch.zeros((n, nkv, hd), device="cuda")
+        vs = torch.zeros((n, nkv, hd), device="cuda")
+        for p in range(n):
+            pg = int(table[s, (p // page) % width])
+            ks[p] = kc[pg, :, p % page, :].float()
+            vs[p] = vc[pg, :, :, p % page].float()
+        dense.append((ks, vs))
+    return kc, vc, table.cuda(), dense
+
+
+def _attn_ref(q, ks, vs, pos, nh, window=None):
+    """q: [nh, hd] float32 at position pos; ks, vs: [len, nkv, hd]."""
+    nkv = ks.shape[1]
+    lo = 0 if not window else max(0, pos + 1 - window)
+    out = torch.zeros_like(q)
+    for h in range(nh):
+        g = h // (nh // nkv)
+        s = ks[lo:pos + 1, g] @ q[h]
+        out[h] = torch.softmax(s, 0) @ vs[lo:pos + 1, g]
+    return out
+
+
+@pytest.mark.parametrize("m,n,kk,mode", [(1, 128, 64, "f32"), (5, 100, 96, "bf16"), (17, 300, 200, "acc"),
+                                          (64, 520, 1032, "bf16"), (100, 1000, 128, "f32"), (300, 384, 1024, "acc"),
+                                          (515, 260, 2048, "bf16")])
+def test_gemm_tc(k, m, n, kk, mode):
+    torch.manual_seed(m + n)
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(n, device="cuda") if m % 2 else None
+    ref = x.float() @ w.float().T + (b if b is not None else 0)
+    if mode == "bf16":
+        out, tol = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16), 2 ** -8
+    elif mode == "f32":
+        out, tol = torch.zeros(m, n, device="cuda"), 1e-5
+    else:
+        out, tol, ref = torch.ones(m, n, device="cuda"), 1e-5, ref + 1
+    k.gemm_tc(x, w, out, b, accumulate=(mode == "acc"))
+    assert (out.float() - ref).abs().max().item() <= tol * ref.abs().max().item() + 1e-6
+    # the plain kernel on the same operands
+    out2 = torch.ones_like(out) if mode == "acc" else torch.zeros_like(out)
+    k.gemm_ref(x, w, out2, b, accumulate=(mode == "acc"))
+    assert (out2.float() - ref).abs().max().item() <= tol * ref.abs().max().item() + 1e-6
+    assert k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+def test_gemm_tc_cluster_split(k, splits):
+    torch.manual_seed(splits)
+    for bn, m in ((16, 3), (32, 29), (64, 64)):
+        x = (torch.randn(m, 1600, device="cuda") * 0.5).bfloat16()
+        w = (torch.randn(333, 1600, device="cuda") * 0.05).bfloat16()
+        ref = x.float() @ w.float().T
+        out = torch.zeros(m, 333, device="cuda")
+        k.gemm_tc(x, w, out, bn=bn, splits=splits)
+        assert (out - ref).abs().max().item() <= 1e-5 * ref.abs().max().item()
+        again = torch.zeros_like(out)
+        k.gemm_tc(x, w, again, bn=bn, splits=splits)
+        assert torch.equal(out, again)                      # added in rank order: the same bits every run
+    assert k.gemm_tc_status() == 0
+
+
+def test_gemm_ref_float32_rows_do_not_depend_on_the_batch(k):
+    torch.manual_seed(1)
+    x = torch.randn(70, 4128 + 32, device="cuda")
+    w = torch.randn(37, 4128 + 32, device="cuda")
+    full = torch.empty(70, 37, device="cuda")
+    k.gemm_ref(x, w, full)
+    assert (full - x.double() @ w.double().T).abs().max().item() < 2e-3
+    for rows in (1, 2, 7):                                   # cf. src/qwen_mtp.rs:748-776
+        part = torch.empty(rows, 37, device="cuda")
+        k.gemm_ref(x[13:13 + rows], w, part)
+        assert torch.equal(part, full[13:13 + rows])
+
+
+def test_gemm_refuses_what_it_cannot_take(k):
+    x = torch.randn(4, 100, device="cuda").bfloat16()
+    w = torch.randn(8, 100, device="cuda").bfloat16()
+    assert not k.gemm_tc_usable(x, w)                        # rows of 200 bytes: not a multiple of 16
+    with pytest.raises(k.KernelError):
+        k.gemm_tc(x, w, torch.empty(4, 8, device="cuda"))
+    out = torch.empty(4, 8, device="cuda", dtype=torch.bfloat16)
+    k.gemm(x, w, out)                                        # the dispatcher falls to the plain kernel
+    assert (out.float() - x.float() @ w.float().T).abs().max().item() < 0.2
+    with pytest.raises(k.KernelError, match="CUDA tensors only"):
+        k.gemm_ref(x.cpu(), w.cpu(), out.cpu())
+
+
+@pytest.mark.parametrize("rows,n,eps", [(3, 80, 1e-5), (17, 4100, 1e-6)])
+def test_rmsnorm_and_gather(k, rows, n, eps):
+    torch.manual_seed(rows)
+    x = torch.randn(rows + 4, n, device="cuda") * 3
+    w = torch.randn(n, device="cuda")
+    ref = x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float() * w
+    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2 ** -8)):
+        out = torch.empty(rows + 4, n, device="cuda", dtype=dt)
+        k.rmsnorm(x, w, out, eps)
+        assert (out.float() - ref).abs().max().item() <= tol * ref.abs().max().item()
+    idx = torch.tensor([rows + 3, 0, 2], dtype=torch.int32, device="cuda")
+    out = torch.empty(3, n, device="cuda")
+    k.rmsnorm(x, w, out, eps, idx)
+    assert torch.allclose(out, ref[idx.long()], rtol=1e-5, atol=1e-5)
+
+
+def test_embedding_and_gated_activation(k):
+    torch.manual_seed(2)
+    table = torch.randn(301, 72, device="cuda").bfloat16()
+    tok = torch.tensor([300, 0, 17, 17], dtype=torch.int32, device="cuda")
+    out = torch.empty(4, 72, device="cuda")
+    k.embed_gather(table, tok, out, 1.5)
+    assert torch.equal(out, table[tok.long()].float() * 1.5)
+    gu = torch.randn(5, 2 * 112, device="cuda")
+    act = torch.empty(5, 112, device="cuda")
+    k.silu_mul(gu, act)
+    g, u = gu[:, :112].double(), gu[:, 112:].double()
+    assert (act - (g / (1 + torch.exp(-g)) * u).float()).abs().max().item() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,rot,nh,nkv", [(48, 24, 5, 1), (16, 16, 4, 2), (128, 128, 8, 2)])
+def test_head_norm_rope_cache(k, dtype, hd, rot, nh, nkv):
+    torch.manual_seed(hd)
+    lengths = [70, 5]
+    kc, vc, table, _ = _paged(2, lengths, nkv, hd, dtype)
+    kc.zero_(); vc.zero_()
+    # the step: sequence 0 appends positions 66..69, sequence 1 positions 0..4
+    tok_seq = torch.tensor([0] * 4 + [1] * 5, dtype=torch.int32, device="cuda")
+    tok_pos = torch.tensor([66, 67, 68, 69, 0, 1, 2, 3, 4], dtype=torch.int32, device="cuda")
+    seq_slot = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
+    t = 9
+    qkv = torch.randn(t, (nh + 2 * nkv) * hd, device="cuda").to(dtype)
+    qw, kw = torch.rand(hd, device="cuda") + 0.5, torch.rand(hd, device="cuda") + 0.5
+    theta, eps, scale = 5e4, 1e-5, hd ** -0.5
+    inv = (1.0 / torch.pow(torch.tensor(theta, dtype=torch.float64), torch.arange(rot // 2, dtype=torch.float64) * 2 / rot)).float().cuda()
+    src = qkv.float().view(t, nh + 2 * nkv, hd).clone()
+    work = qkv.clone()
+    k.head_norm_rope_cache(work, nh, nkv, hd, rot, qw, kw, eps, inv, scale, tok_pos, tok_seq, seq_slot, table, 64, kc, vc,
+                           k.FLAG_NORM | k.FLAG_ROPE | k.FLAG_CACHE | k.FLAG_INPLACE)
+
+    def ref_head(v, w, pos, s):
+        v = v * torch.rsqrt((v.double() ** 2).mean() + eps).float() * w
+        ang = (torch.tensor(float(pos), device="cuda") * inv).double()
+        a, b = v[:rot // 2].double(), v[rot // 2:rot].double()
+        out = v.double().clone()
+        out[:rot // 2] = a * torch.cos(ang) - b * torch.sin(ang)
+        out[rot // 2:rot] = b * torch.cos(ang) + a * torch.sin(ang)
+        return (out * s).float()
+
+    tol = 1e-5 if dtype == torch.float32 else 2 ** -7
+    got = work.float().view(t, nh + 2 * nkv, hd)
+    for i in range(t):
+        pos, slot = int(tok_pos[i]), int(tok_seq[i])
+        page = int(table[slot, pos // 64])
+        for h in range(nh):
+            assert (got[i, h] - ref_head(src[i, h], qw, pos, scale)).abs().max().item() <= tol * 4
+        for h in range(nkv):
+            want = ref_head(src[i, nh + h], kw, pos, 1.0)
+            assert (got[i, nh + h] - want).abs().max().item() <= tol * 4
+            assert (kc[page, h, pos % 64].float() - want).abs().max().item() <= tol * 4
+            assert torch.equal(vc[page, h, :, pos % 64].float(), src[i, nh + nkv + h])     # values are cached raw
+    assert float(kc[0].abs().sum()) == 0.0                                                    # nothing strays into page 0
+
+
+@pytest.mark.parametrize("hd,nh,nkv,window", [(16, 4, 2, None), (32, 6, 3, 40), (48, 5, 1, None), (128, 8, 2, 100),
+                                               (64, 12, 1, None), (128, 32, 1, None)])
+def test_attention_kernels_against_plain(k, hd, nh, nkv, window):
+    """The plain kernel in both precisions and the decode kernel (1 and several shares), with a
+    planted far key: one key far back gets a score that stands out, so a kernel that drops or
+    misplaces a block of keys fails."""
+    torch.manual_seed(hd + nh)
+    lengths = [257, 64, 1, 131]
+    for dtype in (torch.float32, torch.bfloat16):
+        kc, vc, table, dense = _paged(4, lengths, nkv, hd, dtype, seed=hd)
+        tok_seq = torch.arange(4, dtype=torch.int32, device="cuda")
+        tok_pos = torch.tensor([n - 1 for n in lengths], dtype=torch.int32, device="cuda")
+        seq_slot = torch.arange(4, dtype=torch.int32, device="cuda")
+        q = (torch.randn(4, nh * hd, device="cuda") * hd ** -0.5).to(dtype)
+        # plant: query head 0 of sequence 0 points at key 3 (or at the window's first key)
+        far = 3 if window is None else max(0, lengths[0] - window)
+        q0 = dense[0][0][far, 0] * (6.0 / hd ** 0.5)
+        q[0, :hd] = q0.to(dtype)
+        ref = torch.stack([_attn_ref(q[i].float().view(nh, hd), *dense[i], lengths[i] - 1, nh, window).view(-1)
+                           for i in range(4)])
+        tol = 2e-5 if dtype == torch.float32 else 2 ** -7
+        out = torch.zeros(4, nh * hd, device="cuda", dtype=dtype)
+        k.attention_ref(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window)
+        assert (out.float() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+        if dtype == torch.bfloat16:
+            for shares in (1, 3, 8):
+                out2 = torch.zeros_like(out)
+                k.attention_decode(q, out2, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, shares)
+                err = (out2.float() - ref).abs().max().item()
+                assert err <= tol * max(1.0, ref.abs().max().item()), f"shares={shares}: {err}"
