@@ -16,9 +16,7 @@
 //
 // Each CTA leaves (m, l, o) per head in scratch; a second kernel merges the shares in order.
 // With one share the first kernel writes the result itself.
-#include <mma.h>
-
-#include "common.cuh"
+#include "mma.cuh"
 
 #ifndef GB_HEAD_DIM
 #define GB_HEAD_DIM 128
@@ -31,26 +29,6 @@ constexpr int WARPS = 8;
 constexpr int KEYS = 32;                       // keys per block
 constexpr float LOG2E = 1.4426950408889634f;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multiple of 16 up to 256");
-
-__device__ __forceinline__ void mma16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-  return *(uint32_t*)&v;
-}
-__device__ __forceinline__ float quad_max(float v) {
-  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
-  return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-}
-__device__ __forceinline__ float quad_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  return v + __shfl_xor_sync(0xffffffffu, v, 2);
-}
 
 // grid (shares, kv heads * head chunks, tokens); block WARPS * 32.
 // part_o: [tokens, nh, shares, HD]; part_ml: [tokens, nh, shares, 2] (m in log2 units, l).

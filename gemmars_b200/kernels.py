@@ -273,6 +273,24 @@ def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos,
         count_launches(1)   # the merge kernel
 
 
+def attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, cu_seqlens, seq_start, seq_slot, window=None):
+    """bfloat16 causal attention of packed prompt tokens (sequence b owns tokens cu_seqlens[b] to
+    cu_seqlens[b + 1], at positions from seq_start[b]) over the paged cache, which already holds
+    the step's own keys and values."""
+    _cuda(q, out, kcache, vcache, page_table, cu_seqlens, seq_start, seq_slot)
+    nkv, hd = kcache.shape[1], kcache.shape[3]
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and vcache.shape[2:] == (hd, page_size)
+    f = _fn("attention_prefill", "gb_attention_prefill",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+            defines=(("GB_HEAD_DIM", hd),))
+    _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+             page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, cu_seqlens.data_ptr(),
+             seq_start.data_ptr(), seq_slot.data_ptr(), seq_slot.numel(), q.shape[0], nh, window or 0, _stream()),
+           "attention_prefill")
+
+
 # --------------------------------------------------------------------------- sampling
 
 def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None):
@@ -312,7 +330,8 @@ def extra_units():
 def attention_units(compute: str, head_dim: int):
     if compute == "float32":
         return [("attention_ref", ())]
-    return [("attention_ref", ()), ("attention_decode", (("GB_HEAD_DIM", head_dim),))]
+    hd = (("GB_HEAD_DIM", head_dim),)
+    return [("attention_ref", ()), ("attention_decode", hd), ("attention_prefill", hd)]
 
 
 def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=None):
@@ -324,6 +343,10 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
         shares = decode_shares(ctx.n_tokens, nh, nkv, ctx.max_total if window is None else min(ctx.max_total, window))
         attention_decode(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                          window, shares)
+        return
+    if q.dtype == torch.bfloat16:
+        attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, ctx.cu_seqlens, ctx.seq_start,
+                          ctx.seq_slot, window)
         return
     attention_ref(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, window)
 

@@ -221,3 +221,36 @@ def test_attention_kernels_against_plain(k, hd, nh, nkv, window):
                 k.attention_decode(q, out2, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, shares)
                 err = (out2.float() - ref).abs().max().item()
                 assert err <= tol * max(1.0, ref.abs().max().item()), f"shares={shares}: {err}"
+
+
+@pytest.mark.parametrize("hd,nh,nkv,window", [(16, 4, 2, None), (32, 6, 3, 40), (48, 5, 1, None), (128, 8, 2, 100),
+                                               (64, 12, 12, None)])
+def test_attention_prefill_against_plain(k, hd, nh, nkv, window):
+    """Packed prompts of unequal lengths, some continuing a sequence that is already cached; every
+    token against the plain statement.  Sequence 1's last query points at a far key."""
+    torch.manual_seed(hd * 3 + nh)
+    starts, news = [0, 130, 63, 5], [100, 77, 1, 64]           # cached before the step, brought by the step
+    lengths = [s + n for s, n in zip(starts, news)]
+    kc, vc, table, dense = _paged(4, lengths, nkv, hd, torch.bfloat16, seed=hd + 1)
+    cu = [0]
+    for n in news:
+        cu.append(cu[-1] + n)
+    t = cu[-1]
+    q = (torch.randn(t, nh * hd, device="cuda") * hd ** -0.5).bfloat16()
+    far = 7 if window is None else lengths[1] - window
+    q[cu[2] - 1, :hd] = (dense[1][0][far, 0] * (6.0 / hd ** 0.5)).bfloat16()
+    tok_seq = torch.tensor([b for b, n in enumerate(news) for _ in range(n)], dtype=torch.int32, device="cuda")
+    tok_pos = torch.tensor([starts[b] + i for b, n in enumerate(news) for i in range(n)], dtype=torch.int32, device="cuda")
+    seq_slot = torch.arange(4, dtype=torch.int32, device="cuda")
+    out = torch.zeros(t, nh * hd, device="cuda", dtype=torch.bfloat16)
+    k.attention_prefill(q, out, nh, kc, vc, table, 64, torch.tensor(cu, dtype=torch.int32, device="cuda"),
+                        torch.tensor(starts, dtype=torch.int32, device="cuda"), seq_slot, window)
+    ref_kernel = torch.zeros_like(out)
+    k.attention_ref(q, ref_kernel, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window)
+    worst = 0.0
+    for i in range(t):
+        b, pos = int(tok_seq[i]), int(tok_pos[i])
+        ref = _attn_ref(q[i].float().view(nh, hd), *dense[b], pos, nh, window).view(-1)
+        worst = max(worst, (out[i].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item()))
+        assert (ref_kernel[i].float() - ref).abs().max().item() <= 2 ** -7 * max(1.0, ref.abs().max().item())
+    assert worst <= 2 ** -7, worst
