@@ -178,6 +178,7 @@ def main():
     ap.add_argument("--fill", choices=["real", "synthetic"], default="real",
                     help="how the cache is brought to the context length before decoding is timed")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--options", default="", help='further engine options, "key=value;key=value"')
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -206,6 +207,8 @@ def main():
     cache_tokens = max_batch * (args.context + 64)
     opts = EngineOptions.parse({"dtype": "bfloat16", "max_batch": str(max_batch), "max_tokens": str(cache_tokens),
                                 "prefill_chunk": "2048"})
+    for pair in filter(None, (p.strip() for p in args.options.split(";"))):
+        opts.set(*[x.strip() for x in pair.split("=", 1)])
     eng = Engine.from_config(cfg, tensors, opts)
     del tensors
     runner, model = eng.runner, eng.model

@@ -47,8 +47,15 @@ class Runner:
                                    self.prefill_chunk, model.act_dtype, self.device)
         self.vocab_size = model.plan.vocab_size
         self.use_graphs = use_graphs
+        self._graphs = {}
+        self._pool = None
         self.steps_run = 0
         self.launch_count = 0
+
+    def _graph_pool(self):
+        if self._pool is None:
+            self._pool = torch.cuda.graph_pool_handle()
+        return self._pool
 
     # ---- sequences
     def open(self) -> int:
@@ -133,6 +140,14 @@ class Runner:
             max_total = max(max_total, start + n)
         cache.sync()
         t, b = len(tokens), len(part)
+        if self.use_graphs and t == b and len(rows) == b and rows == list(range(b)):
+            # every sequence brings one token and wants its logits: replay the captured step
+            logits = self._decode_graph(tokens, tok_pos, seq_slot, seq_start, max_total)
+            if dest == list(range(dest[0], dest[0] + b)):
+                out[dest[0]:dest[0] + b].copy_(logits)
+            else:
+                out[torch.tensor(dest, device=self.device)] = logits
+            return
         host = torch.tensor(tokens + tok_pos + tok_seq + seq_slot + seq_start + seq_len + cu + rows,
                             dtype=torch.int32).pin_memory()
         dev = host.to(self.device, non_blocking=True)
@@ -158,3 +173,99 @@ class Runner:
                 out[dest[0]:dest[0] + len(dest)].copy_(logits)
             else:
                 out[torch.tensor(dest, device=self.device)] = logits
+
+    # ---- decode steps replayed from CUDA graphs
+    def _decode_graph(self, tokens, tok_pos, seq_slot, seq_start, max_total):
+        """One token per sequence through a captured graph.  The batch is padded to a power of
+        two with rows that belong to no sequence: they use the page table's spare row, write into
+        page 0 and read nothing that a real row reads, so they change no result."""
+        b = len(tokens)
+        bp = 1
+        while bp < b:
+            bp *= 2
+        len_bucket = 256
+        while len_bucket < max_total:
+            len_bucket *= 2
+        key = (bp, len_bucket)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph(self, bp, len_bucket)
+        return g.run(tokens, tok_pos, seq_slot, seq_start)[:b]
+
+
+class _DecodeGraph:
+    """A captured decode step for a padded batch of ``bp`` rows and sequences up to ``len_bucket``
+    long.  Index tensors live at fixed addresses; each run copies the step's values into them
+    from pinned host memory and replays."""
+
+    RING = 4
+
+    def __init__(self, runner: "Runner", bp: int, len_bucket: int):
+        from .. import kernels
+        self.runner, self.bp = runner, bp
+        dev = runner.device
+        self.n = 8 * bp + 1
+        self.meta = torch.zeros(self.n, dtype=torch.int32, device=dev)
+        self.host = [torch.zeros(self.n, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        m, o = self.meta, 0
+
+        def take(n):
+            nonlocal o
+            v = m[o:o + n]
+            o += n
+            return v
+
+        self.d_tokens, self.d_pos, self.d_seq = take(bp), take(bp), take(bp)
+        self.d_slot, self.d_start, self.d_len, self.d_cu, self.d_rows = take(bp), take(bp), take(bp), take(bp + 1), take(bp)
+        pad_slot = runner.cache.n_slots
+        fixed = torch.zeros(self.n, dtype=torch.int32)
+        fixed[2 * bp:3 * bp] = torch.arange(bp)            # tok_seq
+        fixed[3 * bp:4 * bp] = pad_slot                     # seq_slot of padding rows
+        fixed[5 * bp:6 * bp] = 1                            # seq_len
+        fixed[6 * bp:7 * bp + 1] = torch.arange(bp + 1)     # cu_seqlens
+        fixed[7 * bp + 1:8 * bp + 1] = torch.arange(bp)     # wanted rows
+        self.fixed = fixed
+        self.meta.copy_(fixed)
+        model = runner.model
+        self.ctx = StepContext(
+            compute=model.compute, act_dtype=model.act_dtype, device=dev, n_tokens=bp, n_seqs=bp,
+            tok_pos=self.d_pos, tok_seq=self.d_seq, seq_slot=self.d_slot, seq_start=self.d_start, seq_len=self.d_len,
+            cu_seqlens=self.d_cu, is_decode=True, max_new=1, max_total=len_bucket, cache=runner.cache,
+            page_size=runner.cache.page_size)
+        # once eagerly (loads the kernels, warms the allocator), then captured
+        torch.cuda.synchronize(dev)
+        self._forward()
+        torch.cuda.synchronize(dev)
+        before = kernels.launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, pool=runner._graph_pool()):
+            self.logits = self._forward()
+        self.launches = kernels.launch_count() - before
+
+    def _forward(self):
+        model = self.runner.model
+        x = model.forward(self.ctx, self.d_tokens)
+        return model.logits(self.ctx, x, self.d_rows)
+
+    def run(self, tokens, tok_pos, seq_slot, seq_start):
+        from .. import kernels
+        b, bp = len(tokens), self.bp
+        i = self.turn
+        self.turn = (i + 1) % self.RING
+        if self.events[i] is not None:
+            self.events[i].synchronize()       # the copy that last read this host buffer is done
+        h = self.host[i]
+        h.copy_(self.fixed)
+        h[0:b] = torch.tensor(tokens, dtype=torch.int32)
+        h[bp:bp + b] = torch.tensor(tok_pos, dtype=torch.int32)
+        h[3 * bp:3 * bp + b] = torch.tensor(seq_slot, dtype=torch.int32)
+        h[4 * bp:4 * bp + b] = torch.tensor(seq_start, dtype=torch.int32)
+        self.meta.copy_(h, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        self.graph.replay()
+        kernels.count_launches(self.launches)
+        return self.logits

@@ -191,7 +191,7 @@ def gemm_tc_tiling(m: int, n: int, k: int):
     return best, 1
 
 
-def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None):
+def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages=4):
     """out = x @ w.T (+ bias) (bfloat16 or float32 out) or out += ... (float32 out), bfloat16
     operands, on the tcgen05 tensor cores."""
     _cuda(x, w, out, bias)
@@ -209,9 +209,41 @@ def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None):
     auto_bn, auto_splits = gemm_tc_tiling(m, n, k)
     f = _fn("gemm_tc", "gb_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+             c_int, c_int, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
+             bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc")
+
+
+def gemm_small_splits(n: int, k: int) -> int:
+    """K splits for the few-token kernel: enough CTAs (tiles of 256 features x splits) for the SMs,
+    while every rank keeps a few 64-wide blocks of the inner dimension."""
+    tiles, kb = -(-n // 256), -(-k // 64)
+    splits = 1
+    while splits < 8 and tiles * splits < 100 and kb // (splits * 2) >= 4:
+        splits *= 2
+    return splits
+
+
+def gemm_tc_small(x, w, out, bias=None, accumulate=False, splits=None, stages=2):
+    """The tensor-core product for at most 64 rows of x (decoding): see gemm_tc for the operands."""
+    _cuda(x, w, out, bias)
+    m, k = x.shape
+    n = w.shape[0]
+    if m > 64:
+        raise KernelError(f"gemm_tc_small takes at most 64 rows, got {m}")
+    assert w.shape[1] == k and w.is_contiguous() and out.shape == (m, n) and out.stride(1) == 1
+    if not gemm_tc_usable(x, w):
+        raise KernelError("gemm_tc_small: operands must be bfloat16 with 16-byte aligned rows")
+    mode = _TC_MODES.get((out.dtype, bool(accumulate)))
+    if mode is None:
+        raise KernelError(f"gemm_tc_small: cannot {'add into' if accumulate else 'store'} {out.dtype}")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+    f = _fn("gemm_tc", "gb_gemm_tc_small",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
              c_int, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
-             bn or auto_bn, splits or auto_splits, _stream()), "gemm_tc")
+             splits or gemm_small_splits(n, k), stages, _stream()), "gemm_tc_small")
 
 
 def gemm_tc_status(reset: bool = True) -> int:
@@ -317,7 +349,12 @@ def gemm(x, w, out, bias=None, accumulate=False):
     tensor cores, except for operands whose rows TMA cannot address (an inner size that is not
     a multiple of 8), which the plain kernel takes."""
     if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w):
-        gemm_tc(x, w, out, bias, accumulate)
+        m, n = x.shape[0], w.shape[0]
+        if 16 < m <= 64 and n < 128 * _SM_COUNT:
+            # a few dozen tokens against a matrix with few row tiles: tokens on the MMA's rows
+            gemm_tc_small(x, w, out, bias, accumulate)
+        else:
+            gemm_tc(x, w, out, bias, accumulate)
     else:
         gemm_ref(x, w, out, bias, accumulate)
 

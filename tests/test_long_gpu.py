@@ -1,0 +1,89 @@
+"""Long decoding, the first tokens of a sequence, and weights made so that faults show: norm
+weights on q and k are scaled up, which makes attention pick single keys hundreds of positions
+back (or right at a window's edge) instead of averaging, so a wrong key, page or slot changes
+the logits by far more than rounding."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+from tiny_configs import TINY_B
+
+pytestmark = pytest.mark.gpu
+
+
+def _model(tmp_path_factory, factor):
+    from gemmars_b200.weights import random_weights, write_safetensors
+    cfg = dict(TINY_B, max_position_embeddings=1024, sliding_window=70)
+    tensors = random_weights(cfg, seed=21)
+    for name in tensors:
+        if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):
+            tensors[name] = (tensors[name].float() * factor).bfloat16()
+    d = str(tmp_path_factory.mktemp("sharp"))
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    pcfg, w = plain.load_folder(d)
+    rng = np.random.default_rng(3)
+    toks = rng.integers(0, cfg["vocab_size"], 330).tolist()
+    ref = plain.forward(pcfg, w, toks)
+    return d, toks, ref
+
+
+@pytest.fixture(scope="module")
+def sharp_model(tmp_path_factory):
+    return _model(tmp_path_factory, 5.0)
+
+
+@pytest.fixture(scope="module")
+def mild_model(tmp_path_factory):
+    return _model(tmp_path_factory, 1.0)
+
+
+# Scores are 25 times larger than with plain random weights (both norms times 5), and an absolute
+# rounding error in a score is a relative error in its probability: the float32 floor is 25 times
+# the usual 1e-5 or so.  A wrong or missing key moves the logits by more than 1e-3 of their size
+# (test_sharp_weights_make_faults_visible), an order of magnitude above this tolerance.
+# bfloat16 rounds q and k to 8 bits, which such scores turn into errors as large as the faults;
+# it runs on the unscaled weights with its usual tolerance, and its attention kernels meet
+# planted far keys in test_kernels_gpu.py, where inputs are the same bfloat16 values on both sides.
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+def test_long_decoding_and_first_tokens(sharp_model, mild_model, dtype, tol):
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, toks, ref = sharp_model if dtype == "float32" else mild_model
+    scale = float(np.abs(ref).max())
+    model = build_model(folder, dtype=dtype)
+    runner = Runner(model, max_tokens=64 * 12, max_batch=2)
+    # the first tokens, one by one from an empty slot, then a long run of single tokens across pages
+    slot = runner.open()
+    rows = []
+    for t in toks[:3]:
+        rows.append(runner.step([StepItem(slot, [t], [0])])[0].cpu().numpy())
+    rows.extend(runner.step([StepItem(slot, toks[3:40], range(37))]).cpu().numpy())
+    for t in toks[40:]:
+        rows.append(runner.step([StepItem(slot, [t], [0])])[0].cpu().numpy())
+    got = np.stack(rows)
+    err = np.abs(got - ref).max(axis=1)
+    worst = int(err.argmax())
+    assert err[worst] <= tol * scale, f"position {worst} is off by {err[worst]:.3e} (scale {scale:.2f})"
+    runner.close(slot)
+    # the same slot and pages again, whole: what the first use left behind must not show
+    slot2 = runner.open()
+    assert slot2 == slot
+    whole = runner.step([StepItem(slot2, toks, range(len(toks)))]).cpu().numpy()
+    assert np.abs(whole - ref).max() <= tol * scale
+    if dtype == "float32":
+        assert np.array_equal(whole, got)
+    runner.close(slot2)
+    assert runner.cache.pages_held() == 0
+
+
+def test_sharp_weights_make_faults_visible(sharp_model):
+    """Sanity of the fixture: dropping one far key changes the oracle's logits far beyond tolerance."""
+    folder, toks, ref = sharp_model
+    pcfg, w = plain.load_folder(folder)
+    changed = plain.forward(pcfg, w, toks[:200] + [(toks[200] + 1) % pcfg["vocab_size"]] + toks[201:])
+    assert np.abs(changed[-1] - ref[-1]).max() > 1e-3 * np.abs(ref).max()
