@@ -257,3 +257,56 @@ GB_EXPORT int gb_attention_decode(const void* q, long long q_stride, void* out, 
   return launch_decode((const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv,
                        tok_pos, tok_seq, seq_slot, ntok, nh, window, shares, part_o, part_ml, stream);
 }
+
+// ------------------------------------------------------------------ the entry point that allocates nothing
+// See attention_decode_static.h.  The shares' partial results go to a fixed array in device
+// memory instead of a buffer from the caller.  Nothing in it has to start at zero: every
+// element the merge kernel reads was written by the first kernel of the same call.
+#include <mutex>
+
+#include "attention_decode_static.h"
+
+namespace {
+
+static __device__ __align__(256) float g_static_scratch[GB_ATTENTION_DECODE_STATIC_FLOATS];
+
+// The array's device address, per device.  In host code the name g_static_scratch stands for a
+// host-side shadow, not for device memory, so its address is asked for once per device, with
+// that device current, and only that pointer is ever handed to a kernel.
+float* static_scratch_address(int* error) {
+  static float* address[64] = {};
+  static std::mutex mu;
+  int dev = -1;
+  *error = (int)cudaGetDevice(&dev);
+  if (*error != 0) return nullptr;
+  if (dev < 0 || dev >= 64) {
+    *error = GB_ERR_ARG;
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!address[dev]) {
+    void* p = nullptr;
+    *error = (int)cudaGetSymbolAddress(&p, g_static_scratch);
+    if (*error != 0) return nullptr;
+    address[dev] = (float*)p;
+  }
+  return address[dev];
+}
+
+}  // namespace
+
+GB_EXPORT int gb_attention_decode_static(const void* q, long long q_stride, void* out, long long out_stride,
+                                         const void* kcache, const void* vcache, const int* page_table,
+                                         int table_width, int page_size, int nkv, int hd, const int* tok_pos,
+                                         const int* tok_seq, const int* seq_slot, int ntok, int nh, int window,
+                                         int shares, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (shares < 1 || nh <= 0) return GB_ERR_SIZE;
+  const unsigned long long need = (unsigned long long)ntok * nh * shares * (HD + 2);
+  if (shares > 1 && need > GB_ATTENTION_DECODE_STATIC_FLOATS) return GB_ERR_STATIC_SCRATCH;
+  int error = 0;
+  float* scratch = static_scratch_address(&error);
+  if (!scratch) return error;
+  return gb_attention_decode(q, q_stride, out, out_stride, kcache, vcache, page_table, table_width, page_size, nkv, hd,
+                             tok_pos, tok_seq, seq_slot, ntok, nh, window, shares, scratch, stream);
+}
