@@ -21,6 +21,9 @@
 #ifndef GB_HEAD_DIM
 #define GB_HEAD_DIM 128
 #endif
+#ifndef GB_DECODE_MIN_CTAS
+#define GB_DECODE_MIN_CTAS 1      // CTAs the compiler must fit on an SM (caps registers per thread)
+#endif
 
 namespace {
 
@@ -33,7 +36,7 @@ static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multip
 // grid (shares, kv heads * head chunks, tokens); block WARPS * 32.
 // part_o: [tokens, nh, shares, HD]; part_ml: [tokens, nh, shares, 2] (m in log2 units, l).
 template <bool UPPER>   // UPPER: more than 8 query heads per chunk (rows 8..15 of the MMA in use)
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, GB_DECODE_MIN_CTAS)
 attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache, PagedKV kv,
                         const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,

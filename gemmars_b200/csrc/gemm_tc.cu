@@ -265,10 +265,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
       tc_wait_ld();
       if (n < N) {
+        if (MODE == EPI_ACCUMULATE_F32) {
+          // all 16 loads first, then the stores: a load after a store to the same array would
+          // wait for it, and the chunk would take 16 round trips to memory instead of one
+          float old[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int m = m0 + c + j;
-          if (m < M) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + b);
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c + j;
+            old[j] = m < M ? ((const float*)y)[(size_t)m * ldy + n] : 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c + j;
+            if (m < M) ((float*)y)[(size_t)m * ldy + n] = old[j] + __uint_as_float(v[j]) + b;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = m0 + c + j;
+            if (m < M) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + b);
+          }
         }
       }
     }

@@ -270,14 +270,16 @@ def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, to
 
 
 def decode_shares(ntok: int, nh: int, nkv: int, longest: int) -> int:
-    """CTAs along the keys per (token, kv head) for the decode attention kernel: enough CTAs to
-    fill the GPU a few times over, while every warp still gets a couple of 32-key blocks."""
+    """CTAs along the keys per (token, kv head) for the decode attention kernel: about one CTA per
+    SM in all (a CTA's fixed work, loading q and merging its warps, is paid once per share; measured
+    at 8,192 keys: 16 shares are best for one sequence, 2 for eight, 1 for sixty-four), and never
+    so many that a warp is left without a 32-key block."""
     rep = nh // nkv
     chunks = -(-rep // 16)
     base = max(1, ntok * nkv * chunks)
     blocks = -(-max(longest, 1) // 32)
-    want = -(-4 * _SM_COUNT // base)
-    return max(1, min(want, blocks // 16, 64))
+    want = (_SM_COUNT + base // 2) // base
+    return max(1, min(want, blocks // 8, 64))
 
 
 def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None,
