@@ -37,7 +37,10 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
-enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2 };
+// EPI_SWIGLU_BF16: W stacks a gate matrix over an up matrix ([2N, K]); the CTA keeps two
+// accumulators (gate rows and up rows of the same 128 features against one tile of x) and
+// writes silu(gate) * up in bfloat16, so the [M, 2N] intermediate never exists.
+enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2, EPI_SWIGLU_BF16 = 3 };
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
 
 __device__ int g_status;   // first failure of any launch; 0 when all waits completed
@@ -125,9 +128,11 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
          ((uint64_t)2 << 61);
 }
 
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 template <int MODE>
 __device__ __forceinline__ void emit(void* y, size_t idx, float v) {
-  if (MODE == EPI_STORE_BF16) ((bf16*)y)[idx] = __float2bfloat16_rn(v);
+  if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16) ((bf16*)y)[idx] = __float2bfloat16_rn(v);
   else if (MODE == EPI_STORE_F32) ((float*)y)[idx] = v;
   else ((float*)y)[idx] += v;
 }
@@ -138,8 +143,11 @@ template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy) {
-  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr bool DUAL = MODE == EPI_SWIGLU_BF16;
+  constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = (DUAL ? 2 : 1) * W_BYTES, B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN, TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
+  static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "tensor memory columns: a power of two up to 512");
   constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -186,6 +194,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         uint8_t* a = smem + s * STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
+        if (DUAL) tma_load_2d(a + W_BYTES, &map_w, (kb_begin + i) * BK, N + n0, &full_bar[s]);   // the up rows
         tma_load_2d(a + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
       }
     }
@@ -203,10 +212,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
+        const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES), udesc = smem_desc(a + W_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)  // 32 bytes further along the swizzled row per step
+        for (int k = 0; k < BK / UMMA_K; ++k) {  // 32 bytes further along the swizzled row per step
           tc_mma(tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+          if (DUAL) tc_mma(tmem + BN, udesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
+        }
         tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
       }
       tc_commit(tmem_bar);         // the accumulator is complete once everything issued has run
@@ -215,7 +226,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 
   // ---------------- epilogue (warps 0-3); the other warps wait at the barriers below
-  float* partial = (float*)smem;   // [BN][BM] float32, over the pipeline stages (idle by then)
+  float* partial = (float*)smem;   // [ACC_COLS][BM] float32, over the pipeline stages (idle by then)
   bool have_acc = false;
   if (warp < 4) {
     if (kb_count > 0) {
@@ -229,7 +240,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (warp < 4) {
       const int f = warp * 32 + lane;
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
+      for (int c = 0; c < (int)ACC_COLS; c += 16) {
         uint32_t v[16];
         if (have_acc) {
           tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
@@ -251,6 +262,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (m >= M) break;
         float acc = partial[c * BM + f];
         for (uint32_t r = 1; r < nsplit; ++r) acc += ld_peer_f32(&partial[c * BM + f], r);
+        if (DUAL) {
+          float up = partial[(BN + c) * BM + f];
+          for (uint32_t r = 1; r < nsplit; ++r) up += ld_peer_f32(&partial[(BN + c) * BM + f], r);
+          acc = silu_mul(acc, up);
+        }
         if (n < N) emit<MODE>(y, (size_t)m * ldy + n, acc + b);
       }
     }
@@ -263,7 +279,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (m0 + c >= M) break;
       uint32_t v[16];
       tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
-      tc_wait_ld();
+      if (DUAL) {
+        uint32_t u[16];
+        tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + BN + c, u);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+      } else {
+        tc_wait_ld();
+      }
       if (n < N) {
         if (MODE == EPI_ACCUMULATE_F32) {
           // all 16 loads first, then the stores: a load after a store to the same array would
@@ -509,9 +533,11 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 template <int BN, int STAGES, int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K, long long ldy,
            int splits, cudaStream_t stream) {
-  constexpr size_t SMEM = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
+  constexpr size_t STAGE = (size_t)NW * BM * BK * 2 + BN * BK * 2;
+  constexpr size_t SMEM = (size_t)STAGES * STAGE + (2 * STAGES + 1) * 8 + 16 + 1024;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
-  static_assert((size_t)BN * BM * 4 <= (size_t)STAGES * (BM * BK * 2 + BN * BK * 2), "partial sums need the stage memory");
+  static_assert(BN > 64 || (size_t)NW * BN * BM * 4 <= (size_t)STAGES * STAGE, "partial sums need the stage memory");
   auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
   static bool configured = false;
   if (!configured) {
@@ -602,7 +628,8 @@ GB_EXPORT int gb_gemm_tc_small(const void* x, const void* w, const float* bias, 
 }
 
 // x: [M, K] bfloat16, rows ldx elements apart; w: [N, K] bfloat16 contiguous; y: [M, N], rows ldy apart.
-// mode: 0 store bfloat16, 1 store float32, 2 add into float32.  bn: tokens per tile (16, 32, 64, 128, 256);
+// mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 w = [gate; up] of 2N rows and
+// y[M, N] = silu(x gate^T) * (x up^T) in bfloat16.  bn: tokens per tile (16, 32, 64, 128, 256);
 // splits: CTAs of a cluster sharing the inner dimension (1, 2, 4, 8; only with bn <= 64);
 // stages: pipeline depth for bn <= 64 (4 or 8; other tiles have a fixed depth).
 // Needs K % 8 == 0, ldx % 8 == 0 and 16-byte aligned x and w (TMA rules).
@@ -613,8 +640,20 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return GB_ERR_ARG;
   if (splits > 1 && bn > 64) return GB_ERR_ARG;
   CUtensorMap mw, mx;
-  if (!tensor_map(&mw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
+  const bool swiglu = mode == EPI_SWIGLU_BF16;   // w is [2N, K]: gate rows, then up rows
+  if (swiglu && bias) return GB_ERR_ARG;
+  if (!tensor_map(&mw, w, (uint64_t)N * (swiglu ? 2 : 1), (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  if (swiglu) {
+    switch (bn) {
+      case 16: return launch<16, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      case 32: return launch<32, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      case 64: return launch<64, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      case 128: return launch<128, 4, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      case 256: return launch<256, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    }
+    return GB_ERR_SIZE;
+  }
   switch (bn) {
     // decoding: `stages` = 4 leaves room for three CTAs on an SM (their tiles then finish together),
     // 8 gives one CTA a deeper pipeline

@@ -34,9 +34,8 @@ class GatedMLP(Part):
         return kernels.gemm_units(self.compute) + [("elementwise", ())]
 
     def forward(self, ctx, h, residual):
-        gu = self.gate_up(h)
         a = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
-        kernels.silu_mul(gu, a)
+        kernels.gemm_swiglu(h, self.gate_up.weight, a)
         self.down.add_into(a, residual)
 
     def weight_bytes(self):

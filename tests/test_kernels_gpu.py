@@ -277,3 +277,23 @@ def test_gemm_tc_small(k, m, n, kk, mode, splits):
     assert k.gemm_tc_status() == 0
     with pytest.raises(k.KernelError):
         k.gemm_tc_small(torch.zeros(65, kk, device="cuda").bfloat16(), w, torch.zeros(65, n, device="cuda"))
+
+
+@pytest.mark.parametrize("m,inter,kk,bn,splits", [(1, 192, 64, None, None), (8, 160, 96, None, None), (40, 1000, 512, None, None),
+                                                  (200, 384, 1024, 128, 1), (300, 520, 256, 256, 1), (64, 640, 4096, 64, 4),
+                                                  (7, 12288 // 8, 4096, 16, 2)])
+def test_gemm_tc_gated(k, m, inter, kk, bn, splits):
+    """silu(x gate^T) * (x up^T) in one kernel against the two-step statement."""
+    torch.manual_seed(m + inter)
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(2 * inter, kk, device="cuda") * 0.08).bfloat16()
+    g = x.float() @ w[:inter].float().T
+    u = x.float() @ w[inter:].float().T
+    ref = g / (1 + torch.exp(-g)) * u
+    out = torch.zeros(m, inter, device="cuda", dtype=torch.bfloat16)
+    k.gemm_tc(x, w, out, swiglu=True, bn=bn, splits=splits)
+    assert (out.float() - ref).abs().max().item() <= 2 ** -8 * ref.abs().max().item() + 1e-6
+    out2 = torch.zeros_like(out)
+    k.gemm_swiglu(x, w, out2)
+    assert torch.equal(out, out2) or (bn is not None)
+    assert k.gemm_tc_status() == 0
