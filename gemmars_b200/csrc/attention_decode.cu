@@ -43,6 +43,8 @@ attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         const int* __restrict__ seq_slot, int nh, int window, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int rows_per_chunk) {
   extern __shared__ float smem[];
+  pdl_release_next();
+  pdl_wait_prior();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int shares = gridDim.x, share = blockIdx.x;
@@ -195,6 +197,8 @@ attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 // Merges the shares of one (token, head) in share order.
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        bf16* __restrict__ out, long long out_stride, int nh, int shares) {
+  pdl_release_next();
+  pdl_wait_prior();
   const int t = blockIdx.x, head = blockIdx.y;
   const size_t base = ((size_t)t * nh + head) * shares;
   float M = -INFINITY;
@@ -223,18 +227,18 @@ int launch_decode(const bf16* q, long long q_stride, bf16* out, long long out_st
     auto k = attention_decode_kernel<false>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return (int)cudaGetLastError();
-    k<<<grid, WARPS * 32, smem, stream>>>(q, q_stride, out, out_stride, kc, vc, kv, tok_pos, tok_seq, seq_slot, nh,
+    gb_launch(k, grid, WARPS * 32, smem, stream, q, q_stride, out, out_stride, kc, vc, kv, tok_pos, tok_seq, seq_slot, nh,
                                           window, part_o, part_ml, rows);
   } else {
     auto k = attention_decode_kernel<true>;
     if (smem > 48 * 1024 && cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return (int)cudaGetLastError();
-    k<<<grid, WARPS * 32, smem, stream>>>(q, q_stride, out, out_stride, kc, vc, kv, tok_pos, tok_seq, seq_slot, nh,
+    gb_launch(k, grid, WARPS * 32, smem, stream, q, q_stride, out, out_stride, kc, vc, kv, tok_pos, tok_seq, seq_slot, nh,
                                           window, part_o, part_ml, rows);
   }
   int rc = gb_launch_status();
   if (rc != 0 || shares == 1) return rc;
-  attention_merge_kernel<<<dim3(ntok, nh), HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, out, out_stride, nh, shares);
+  gb_launch(attention_merge_kernel, dim3(ntok, nh), HD >= 128 ? 128 : 64, 0, stream, part_o, part_ml, out, out_stride, nh, shares);
   return gb_launch_status();
 }
 

@@ -31,6 +31,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, long long q_stride, bf16* _
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache, PagedKV kv,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_slot, int n_seqs, int nh, int window, int heads_per_cta) {
+  pdl_release_next();
+  pdl_wait_prior();
   // ---- which sequence and which 64-token tile of it
   int b = 0, tile = blockIdx.x;
   for (; b < n_seqs; ++b) {
@@ -179,7 +181,7 @@ GB_EXPORT int gb_attention_prefill(const void* q, long long q_stride, void* out,
   const int heads_per_cta = rep < RH ? rep : RH;
   const int chunks = (rep + heads_per_cta - 1) / heads_per_cta;
   dim3 grid((ntok + TILE - 1) / TILE + n_seqs, nkv * chunks);
-  attention_prefill_kernel<<<grid, MT * heads_per_cta * 32, 0, stream>>>(
+  gb_launch(attention_prefill_kernel, grid, MT * heads_per_cta * 32, 0, stream,
       (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)kcache, (const bf16*)vcache, kv, cu_seqlens,
       seq_start, seq_slot, n_seqs, nh, window, heads_per_cta);
   return gb_launch_status();

@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(CHUNK) attention_ref_kernel(
     const T* __restrict__ kcache, const T* __restrict__ vcache, PagedKV kv, const int* __restrict__ tok_pos,
     const int* __restrict__ tok_seq, const int* __restrict__ seq_slot, int nh, int window) {
   extern __shared__ float smem[];
+  pdl_release_next();
+  pdl_wait_prior();
   const int hd = kv.head_dim;
   float* qs = smem;                    // [hd]
   float* p = qs + hd;                  // [CHUNK]
@@ -80,11 +82,11 @@ GB_EXPORT int gb_attention_ref(const void* q, long long q_stride, void* out, lon
   const size_t smem = (size_t)(hd + CHUNK + 34) * sizeof(float) + CHUNK * sizeof(size_t) + 8;
   dim3 grid(ntok, nh);
   if (dtype == GB_F32)
-    attention_ref_kernel<float><<<grid, CHUNK, smem, stream>>>((const float*)q, q_stride, (float*)out, out_stride,
+    gb_launch(attention_ref_kernel<float>, grid, CHUNK, smem, stream, (const float*)q, q_stride, (float*)out, out_stride,
                                                               (const float*)kcache, (const float*)vcache, kv,
                                                               tok_pos, tok_seq, seq_slot, nh, window);
   else if (dtype == GB_BF16)
-    attention_ref_kernel<bf16><<<grid, CHUNK, smem, stream>>>((const bf16*)q, q_stride, (bf16*)out, out_stride,
+    gb_launch(attention_ref_kernel<bf16>, grid, CHUNK, smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                                                              (const bf16*)kcache, (const bf16*)vcache, kv, tok_pos,
                                                              tok_seq, seq_slot, nh, window);
   else

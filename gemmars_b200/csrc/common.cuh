@@ -91,3 +91,40 @@ struct PagedKV {
 };
 
 static inline int gb_launch_status() { return (int)cudaGetLastError(); }
+
+// Programmatic dependent launch.  Every kernel of the package is launched so that it may start
+// while the kernel before it in the stream is still running; it then does what does not depend
+// on that kernel (set-up, prefetch of weights) and calls pdl_wait_prior() before it touches
+// anything the earlier kernel wrote, or writes anything the earlier kernel may still read.
+// pdl_release_next() lets the kernel after this one start in the same way.  Off by default
+// (GB_PDL=0: plain launches): measured on the Qwen3-8B decode step it gains 4% at batch 1 and
+// loses 5% at batch 8 and 13% at batch 64, where the early weight prefetch of the next kernels
+// competes with the running attention kernel.  -DGB_PDL=1 turns it on; =2 without early release.
+#ifndef GB_PDL
+#define GB_PDL 0
+#endif
+__device__ __forceinline__ void pdl_wait_prior() {
+#if GB_PDL
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_release_next() {
+#if GB_PDL == 1   // GB_PDL=2: no early release; the next kernel starts as this one's blocks finish
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+
+template <typename Kernel, typename... Args>
+static inline void gb_launch(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = GB_PDL ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<Args&&>(args)...);
+}

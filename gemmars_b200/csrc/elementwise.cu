@@ -12,6 +12,8 @@
 template <typename W>
 __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __restrict__ tok, float* __restrict__ x,
                                     int hidden, int vocab, float scale) {
+  pdl_release_next();
+  pdl_wait_prior();
   const int t = blockIdx.x;
   int id = tok[t];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are checked on the host; never read outside
@@ -25,9 +27,9 @@ GB_EXPORT int gb_embed_gather(const void* table, int table_dtype, const int* tok
   if (ntok <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == GB_F32)
-    embed_gather_kernel<float><<<ntok, threads, 0, stream>>>((const float*)table, tok, x, hidden, vocab, scale);
+    gb_launch(embed_gather_kernel<float>, ntok, threads, 0, stream, (const float*)table, tok, x, hidden, vocab, scale);
   else if (table_dtype == GB_BF16)
-    embed_gather_kernel<bf16><<<ntok, threads, 0, stream>>>((const bf16*)table, tok, x, hidden, vocab, scale);
+    gb_launch(embed_gather_kernel<bf16>, ntok, threads, 0, stream, (const bf16*)table, tok, x, hidden, vocab, scale);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();
@@ -40,6 +42,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, T* __restrict__ out,
                                const int* __restrict__ rows_index, int n, float eps) {
   __shared__ float scratch[33];
+  pdl_release_next();
+  pdl_wait_prior();
   const int r = blockIdx.x;
   const float* row = x + (size_t)(rows_index ? rows_index[r] : r) * n;
   float ss = 0.f;
@@ -55,9 +59,9 @@ GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtyp
   if (rows <= 0) return 0;
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
   if (out_dtype == GB_F32)
-    rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(x, w, (float*)out, rows_index, n, eps);
+    gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps);
   else if (out_dtype == GB_BF16)
-    rmsnorm_kernel<bf16><<<rows, threads, 0, stream>>>(x, w, (bf16*)out, rows_index, n, eps);
+    gb_launch(rmsnorm_kernel<bf16>, rows, threads, 0, stream, x, w, (bf16*)out, rows_index, n, eps);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();
@@ -79,6 +83,8 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
                                             const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                             const int* __restrict__ seq_slot, PagedKV kv, T* __restrict__ kcache,
                                             T* __restrict__ vcache, int flags) {
+  pdl_release_next();
+  pdl_wait_prior();
   const int lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
   const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -153,11 +159,11 @@ GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, in
   const int wpb = 4;
   const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
   if (dtype == GB_F32)
-    head_norm_rope_cache_kernel<float><<<grid, wpb * 32, 0, stream>>>(
+    gb_launch(head_norm_rope_cache_kernel<float>, grid, wpb * 32, 0, stream, 
         (float*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
         (float*)kcache, (float*)vcache, flags);
   else if (dtype == GB_BF16)
-    head_norm_rope_cache_kernel<bf16><<<grid, wpb * 32, 0, stream>>>(
+    gb_launch(head_norm_rope_cache_kernel<bf16>, grid, wpb * 32, 0, stream, 
         (bf16*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
         (bf16*)kcache, (bf16*)vcache, flags);
   else
@@ -169,6 +175,8 @@ GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, in
 // out[t, i] = silu(gu[t, i]) * gu[t, inter + i];  silu(a) = a / (1 + exp(-a)).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total, int inter) {
+  pdl_release_next();
+  pdl_wait_prior();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long t = idx / inter;
@@ -182,9 +190,9 @@ GB_EXPORT int gb_silu_mul(const void* gu, void* out, int dtype, int ntok, int in
   if (total <= 0) return 0;
   const unsigned grid = (unsigned)((total + 255) / 256);
   if (dtype == GB_F32)
-    silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+    gb_launch(silu_mul_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)out, total, inter);
   else if (dtype == GB_BF16)
-    silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, total, inter);
+    gb_launch(silu_mul_kernel<bf16>, grid, 256, 0, stream, (const bf16*)gu, (bf16*)out, total, inter);
   else
     return GB_ERR_DTYPE;
   return gb_launch_status();

@@ -16,6 +16,8 @@ template <typename TI, typename TO, int MODE>
 __global__ void __launch_bounds__(256) gemm_ref_kernel(const TI* __restrict__ x, const TI* __restrict__ w,
                                                        const float* __restrict__ bias, TO* __restrict__ y, int M,
                                                        int N, int K, long long ldx, long long ldy) {
+  pdl_release_next();
+  pdl_wait_prior();
   __shared__ float xs[BK][BM + 4];
   __shared__ float ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -72,7 +74,7 @@ GB_EXPORT int gb_gemm_ref(const void* x, const void* w, int in_dtype, const floa
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (mode == OUT_ACCUMULATE_F32 && out_dtype != GB_F32) return GB_ERR_DTYPE;
 #define LAUNCH(TI, TO, MODE) \
-  gemm_ref_kernel<TI, TO, MODE><<<grid, 256, 0, stream>>>((const TI*)x, (const TI*)w, bias, (TO*)y, M, N, K, ldx, ldy)
+  gb_launch(gemm_ref_kernel<TI, TO, MODE>, grid, 256, 0, stream, (const TI*)x, (const TI*)w, bias, (TO*)y, M, N, K, ldx, ldy)
   if (in_dtype == GB_F32) {
     if (out_dtype != GB_F32) return GB_ERR_DTYPE;
     if (mode == OUT_ACCUMULATE_F32) LAUNCH(float, float, OUT_ACCUMULATE_F32);

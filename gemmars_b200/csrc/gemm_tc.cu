@@ -163,6 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb_begin = (int)((long long)kb_total * split / nsplit), kb_end = (int)((long long)kb_total * (split + 1) / nsplit);
   const int kb_count = kb_end - kb_begin;
 
+  pdl_release_next();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -185,9 +186,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-      for (int i = 0; i < kb_count; ++i) {
+      // the weights do not depend on the kernel before this one: the first stages' W tiles are
+      // asked for at once, x only after that kernel has finished
+      const int pre = kb_count < STAGES ? kb_count : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        uint8_t* a = smem + i * STAGE_BYTES;
+        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+        tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+        if (DUAL) tma_load_2d(a + W_BYTES, &map_w, (kb_begin + i) * BK, N + n0, &full_bar[i]);   // the up rows
+      }
+      pdl_wait_prior();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full_bar[i]);
+      for (int i = pre; i < kb_count; ++i) {
         const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
+        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
           atomicCAS(&g_status, ST_OK, ST_TIMEOUT_EMPTY);
           break;
         }
@@ -234,9 +247,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!have_acc && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
     }
     tc_fence_after();
+    pdl_wait_prior();   // y may be read (accumulate) and is written: not before the kernel before is done
   }
   if (nsplit > 1) {
-    // every rank publishes its partial sums; rank 0 adds them in rank order
+    // every rank publishes its partial sums, then adds a share of the tokens over all ranks
     if (warp < 4) {
       const int f = warp * 32 + lane;
 #pragma unroll 1
@@ -254,23 +268,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     cluster_sync();
-    if (split == 0 && warp < 4) {
+    if (warp < 4) {
+      // every rank adds its own share of the tile's tokens over all ranks, in rank order; the
+      // loads of one token are all in flight together
       const int f = warp * 32 + lane, n = n0 + f;
       const float b = (bias && n < N) ? bias[n] : 0.f;
-      for (int c = 0; c < BN; ++c) {
+      const int cols = BN / (int)nsplit, c0 = (int)split * cols;
+#pragma unroll 2
+      for (int c = c0; c < c0 + cols; ++c) {
         const int m = m0 + c;
         if (m >= M) break;
-        float acc = partial[c * BM + f];
-        for (uint32_t r = 1; r < nsplit; ++r) acc += ld_peer_f32(&partial[c * BM + f], r);
+        float v[8], u[8];
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) {
+          v[r] = r < nsplit ? ld_peer_f32(&partial[c * BM + f], r) : 0.f;
+          if (DUAL) u[r] = r < nsplit ? ld_peer_f32(&partial[(BN + c) * BM + f], r) : 0.f;
+        }
+        float acc = v[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r) acc += v[r];
         if (DUAL) {
-          float up = partial[(BN + c) * BM + f];
-          for (uint32_t r = 1; r < nsplit; ++r) up += ld_peer_f32(&partial[(BN + c) * BM + f], r);
+          float up = u[0];
+#pragma unroll
+          for (int r = 1; r < 8; ++r) up += u[r];
           acc = silu_mul(acc, up);
         }
         if (n < N) emit<MODE>(y, (size_t)m * ldy + n, acc + b);
       }
     }
-    cluster_sync();  // peers keep their shared memory until rank 0 has read it
+    cluster_sync();  // every rank keeps its shared memory until the others have read it
   } else if (warp < 4 && have_acc) {
     const int f = warp * 32 + lane, n = n0 + f;
     const float b = (bias && n < N) ? bias[n] : 0.f;
@@ -350,6 +376,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
   const int kb_begin = (int)((long long)kb_total * split / nsplit), kb_end = (int)((long long)kb_total * (split + 1) / nsplit);
   const int kb_count = kb_end - kb_begin;
 
+  pdl_release_next();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -371,9 +398,16 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-      for (int i = 0; i < kb_count; ++i) {
+      const int pre = kb_count < STAGES ? kb_count : STAGES;
+      for (int i = 0; i < pre; ++i) {   // weights first: they do not depend on the kernel before
+        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
+      }
+      pdl_wait_prior();
+      for (int i = 0; i < pre; ++i) tma_load_2d(smem + i * STAGE_BYTES, &map_x, (kb_begin + i) * BK, 0, &full_bar[i]);
+      for (int i = pre; i < kb_count; ++i) {
         const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
+        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
           atomicCAS(&g_status, ST_OK, ST_TIMEOUT_EMPTY);
           break;
         }
@@ -415,6 +449,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
       if (!have_acc && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
     }
     tc_fence_after();
+    pdl_wait_prior();   // y may be read (accumulate) and is written: not before the kernel before is done
   }
   if (nsplit > 1) {
     float* partial = (float*)smem;                // [rows][SM_PAD], rows = min(M, 128)
@@ -550,13 +585,15 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = GB_PDL ? 2 : 1;
   return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, bias, y, M, N, K, ldy);
 }
 
@@ -589,13 +626,15 @@ int launch_small(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = SMEM;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = splits;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = GB_PDL ? 2 : 1;
   return (int)cudaLaunchKernelEx(&cfg, kernel, mx, mw, bias, y, M, N, K, ldy);
 }
 

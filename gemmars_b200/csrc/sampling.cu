@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
   __shared__ int red_i[32];
   __shared__ unsigned sh_prefix;
   __shared__ int sh_remaining, sh_count;
+  pdl_release_next();
+  pdl_wait_prior();
   const int row = blockIdx.x, tid = threadIdx.x;
   const float* l = logits + (size_t)row * stride;
   const float temp = temperature ? temperature[row] : 0.f;
@@ -188,6 +190,6 @@ GB_EXPORT int gb_sample(const float* logits, long long stride, int rows, int voc
   if (rows <= 0) return 0;
   if (vocab <= 0) return GB_ERR_SIZE;
   if (temperature && (!top_k || !top_p || !uniform)) return GB_ERR_ARG;
-  sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, stride, vocab, temperature, top_k, top_p, uniform, out);
+  gb_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, stride, vocab, temperature, top_k, top_p, uniform, out);
   return gb_launch_status();
 }
