@@ -350,6 +350,38 @@ def attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, cu_seql
            "attention_prefill")
 
 
+TC_PREFILL_HEAD_DIMS = (64, 128)
+
+
+def attention_prefill_tc(q, out, nh, kcache, vcache, page_table, page_size, cu_seqlens, seq_start, seq_slot,
+                         window=None):
+    """As attention_prefill, on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory); head
+    sizes 64 and 128."""
+    _cuda(q, out, kcache, vcache, page_table, cu_seqlens, seq_start, seq_slot)
+    nkv, hd = kcache.shape[1], kcache.shape[3]
+    if hd not in TC_PREFILL_HEAD_DIMS:
+        raise KernelError(f"attention_prefill_tc: head size {hd} is not supported (64 or 128)")
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and vcache.shape[2:] == (hd, page_size)
+    assert kcache.is_contiguous() and vcache.is_contiguous() and kcache.shape[0] == vcache.shape[0]
+    f = _fn("attention_prefill_tc", "gb_attention_prefill_tc",
+            [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int,
+             c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+            defines=(("GB_HEAD_DIM", hd),))
+    _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+             kcache.shape[0], page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, cu_seqlens.data_ptr(),
+             seq_start.data_ptr(), seq_slot.data_ptr(), seq_slot.numel(), q.shape[0], nh, window or 0, _stream()),
+           "attention_prefill_tc")
+
+
+def attention_prefill_tc_status(head_dim: int, reset: bool = True) -> int:
+    """0, or the code of the first bounded wait that ran out in attention_prefill_tc (synchronizes)."""
+    lib = build.load("attention_prefill_tc", (("GB_HEAD_DIM", head_dim),))
+    lib.gb_attention_prefill_tc_status.argtypes = [c_int]
+    lib.gb_attention_prefill_tc_status.restype = c_int
+    return lib.gb_attention_prefill_tc_status(1 if reset else 0)
+
+
 # --------------------------------------------------------------------------- sampling
 
 def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None):
@@ -395,7 +427,8 @@ def attention_units(compute: str, head_dim: int):
     if compute == "float32":
         return [("attention_ref", ())]
     hd = (("GB_HEAD_DIM", head_dim),)
-    return [("attention_ref", ()), ("attention_decode", hd), ("attention_prefill", hd)]
+    prefill = "attention_prefill_tc" if head_dim in (64, 128) else "attention_prefill"
+    return [("attention_ref", ()), ("attention_decode", hd), (prefill, hd)]
 
 
 def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=None):
@@ -409,8 +442,8 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
                          window, shares)
         return
     if q.dtype == torch.bfloat16:
-        attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, ctx.cu_seqlens, ctx.seq_start,
-                          ctx.seq_slot, window)
+        prefill = attention_prefill_tc if kcache.shape[3] in TC_PREFILL_HEAD_DIMS else attention_prefill
+        prefill(q, out, nh, kcache, vcache, page_table, page_size, ctx.cu_seqlens, ctx.seq_start, ctx.seq_slot, window)
         return
     attention_ref(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, window)
 

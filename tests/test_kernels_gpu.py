@@ -297,3 +297,36 @@ def test_gemm_tc_gated(k, m, inter, kk, bn, splits):
     k.gemm_swiglu(x, w, out2)
     assert torch.equal(out, out2) or (bn is not None)
     assert k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("hd,nh,nkv,window", [(64, 4, 2, None), (128, 8, 2, 100), (64, 6, 6, 70), (128, 4, 1, None)])
+def test_attention_prefill_tc_against_plain(k, hd, nh, nkv, window):
+    """The tcgen05 prompt kernel: packed prompts of unequal lengths (one longer than two tiles,
+    one continuing a cached sequence across pages, single tokens), every token against the plain
+    statement; a query at the end of a long sequence points at a far key."""
+    torch.manual_seed(hd + nh)
+    starts, news = [0, 130, 63, 5, 0], [300, 77, 1, 128, 129]
+    lengths = [s + n for s, n in zip(starts, news)]
+    kc, vc, table, dense = _paged(5, lengths, nkv, hd, torch.bfloat16, seed=hd + 2)
+    cu = [0]
+    for n in news:
+        cu.append(cu[-1] + n)
+    t = cu[-1]
+    q = (torch.randn(t, nh * hd, device="cuda") * hd ** -0.5).bfloat16()
+    far = 7 if window is None else lengths[0] - window
+    q[cu[1] - 1, :hd] = (dense[0][0][far, 0] * (6.0 / hd ** 0.5)).bfloat16()
+    tok_seq = [b for b, n in enumerate(news) for _ in range(n)]
+    tok_pos = [starts[b] + i for b, n in enumerate(news) for i in range(n)]
+    seq_slot = torch.arange(5, dtype=torch.int32, device="cuda")
+    out = torch.zeros(t, nh * hd, device="cuda", dtype=torch.bfloat16)
+    k.attention_prefill_tc(q, out, nh, kc, vc, table, 64, torch.tensor(cu, dtype=torch.int32, device="cuda"),
+                           torch.tensor(starts, dtype=torch.int32, device="cuda"), seq_slot, window)
+    torch.cuda.synchronize()
+    assert k.attention_prefill_tc_status(hd) == 0
+    worst, where = 0.0, None
+    for i in range(t):
+        ref = _attn_ref(q[i].float().view(nh, hd), *dense[tok_seq[i]], tok_pos[i], nh, window).view(-1)
+        err = (out[i].float() - ref).abs().max().item() / max(1.0, ref.abs().max().item())
+        if err > worst:
+            worst, where = err, (tok_seq[i], tok_pos[i])
+    assert worst <= 2 ** -7, (worst, where)
