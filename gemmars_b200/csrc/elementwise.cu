@@ -46,18 +46,42 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   pdl_wait_prior();
   const int r = blockIdx.x;
   const float* row = x + (size_t)(rows_index ? rows_index[r] : r) * n;
+  T* o = out + (size_t)r * n;
+  // four elements at a time when the row allows it (rows of x and out are then 16-byte aligned);
+  // the order of the additions depends on n and the block size alone
+  if ((n & 3) == 0) {
+    const float4* row4 = (const float4*)row;
+    const float4* w4 = (const float4*)w;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      const float4 v = row4[i];
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+      const float4 v = row4[i], g = w4[i];
+      const float a = v.x * inv * g.x, b = v.y * inv * g.y, c = v.z * inv * g.z, d = v.w * inv * g.w;
+      if (sizeof(T) == 4) {
+        ((float4*)o)[i] = make_float4(a, b, c, d);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        ((uint2*)o)[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) ss += row[i] * row[i];
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-  T* o = out + (size_t)r * n;
   for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>(row[i] * inv * w[i]);
 }
 
 GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
                          int n, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
+  const int threads = n >= 4096 ? 512 : (n >= 1024 ? 256 : 128);
   if (out_dtype == GB_F32)
     gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps);
   else if (out_dtype == GB_BF16)
