@@ -49,6 +49,10 @@ __device__ __forceinline__ void emit(void* y, size_t idx, float v) {
   else ((float*)y)[idx] += v;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // ------------------------------------------------------------------ the kernel
 // grid = (token tiles, feature tiles, K splits); a cluster spans the K splits of one tile.
 template <int BN, int STAGES, int MODE>
@@ -249,6 +253,177 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           }
         }
       }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+// ------------------------------------------------------------------ the persistent kernel for prompts
+// One CTA per SM walks the output tiles (token tile fastest, so the CTAs that run together
+// share the same rows of W).  The accumulator in tensor memory is double-buffered: while the
+// four epilogue warps read tile i out of one buffer and store it, the MMA warp already fills the
+// other with tile i + 1, and the TMA warp runs ahead through the shared-memory stages across
+// tile borders.  Gated mode keeps two accumulators per buffer (BN <= 128).
+template <int BN, int STAGES, int MODE>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                          const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy) {
+  constexpr bool DUAL = MODE == EPI_SWIGLU_BF16;
+  constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = (DUAL ? 2 : 1) * W_BYTES, B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN, TMEM_COLS = 2 * ACC_COLS;
+  static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "two accumulator buffers: 256 or 512 columns");
+  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;     // 2: the MMA warp has finished a tile in that buffer
+  uint64_t* acc_empty = acc_full + 2;          // 2: the epilogue warps have read it out
+  uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + BN - 1) / BN, tiles_n = (N + BM - 1) / BM, tiles = tiles_m * tiles_n;
+  const int kb_total = (K + BK - 1) / BK;
+
+  pdl_release_next();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- TMA producer: all of this CTA's tiles, one stream of stages
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      pdl_wait_prior();
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+        const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
+            atomicCAS(&g_status, ST_OK, ST_TIMEOUT_EMPTY);
+            ok = false;
+            break;
+          }
+          uint8_t* a = smem + s * STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+          tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
+          if (DUAL) tma_load_2d(a + W_BYTES, &map_w, kb * BK, N + n0, &full_bar[s]);
+          tma_load_2d(a + A_BYTES, &map_x, kb * BK, m0, &full_bar[s]);
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 5) {
+    // ---------------- MMA issue
+    if (lane == 0) {
+      uint32_t it = 0, i = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
+        const uint32_t b = i & 1;
+        if (i >= 2 && !mbar_wait(&acc_empty[b], ((i >> 1) - 1) & 1)) {   // the epilogue has read this buffer out
+          atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d = tmem + b * ACC_COLS;
+        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+          const uint32_t s = it % STAGES;
+          if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
+            atomicCAS(&g_status, ST_OK, ST_TIMEOUT_FULL);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES), udesc = smem_desc(a + W_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            tc_mma(d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+            if (DUAL) tc_mma(d + BN, udesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);
+        }
+        tc_commit(&acc_full[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue warps: lane = feature, column = token
+    pdl_wait_prior();
+    const int f = warp * 32 + lane;
+    uint32_t i = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
+      const uint32_t b = i & 1;
+      const int m0 = (t % tiles_m) * BN, n0 = (t / tiles_m) * BM, n = n0 + f;
+      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1))) {
+        if (lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
+        break;
+      }
+      tc_fence_after();
+      const float bv = (bias && n < N) ? bias[n] : 0.f;
+      const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16) + b * ACC_COLS;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        if (m0 + c >= M) break;
+        uint32_t v[16];
+        tc_ld16(acc + c, v);
+        if (DUAL) {
+          uint32_t u[16];
+          tc_ld16(acc + BN + c, u);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+        } else {
+          tc_wait_ld();
+        }
+        if (n < N) {
+          if (MODE == EPI_ACCUMULATE_F32) {
+            float old[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c + j;
+              old[j] = m < M ? ((const float*)y)[(size_t)m * ldy + n] : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c + j;
+              if (m < M) ((float*)y)[(size_t)m * ldy + n] = old[j] + __uint_as_float(v[j]) + bv;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = m0 + c + j;
+              if (m < M) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + bv);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
   }
   tc_fence_before();
@@ -461,6 +636,24 @@ int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const fl
   return GB_ERR_ARG;
 }
 
+template <int BN, int STAGES, int MODE>
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K,
+                      long long ldy, int ctas, cudaStream_t stream) {
+  constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
+  constexpr size_t SMEM = (size_t)STAGES * ((size_t)NW * BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
+  auto kernel = gemm_tc_persistent_kernel<BN, STAGES, MODE>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
+      return (int)cudaGetLastError();
+    configured = true;
+  }
+  const int tiles = ((M + BN - 1) / BN) * ((N + BM - 1) / BM);
+  gb_launch(kernel, dim3(tiles < ctas ? tiles : ctas), dim3(THREADS), SMEM, stream, mw, mx, bias, y, M, N, K, ldy);
+  return gb_launch_status();
+}
+
 template <int STAGES, int MODE>
 int launch_small(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* y, int M, int N, int K,
                  long long ldy, int splits, cudaStream_t stream) {
@@ -558,10 +751,45 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
     case 64:
       return stages == 8 ? launch_mode<64, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
                          : launch_mode<64, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
-    case 128: return launch_mode<128, 6>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case 128:   // stages = 3: two CTAs fit an SM, and one's epilogue runs under the other's MMAs
+      return stages == 3 ? launch_mode<128, 3>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
+                         : launch_mode<128, 6>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
     case 256: return launch_mode<256, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
   }
   return GB_ERR_SIZE;
+}
+
+// The same product for prompts (M > 64): one CTA per SM walks the tiles and the epilogue of a tile
+// runs under the MMAs of the next.  mode as gb_gemm_tc; bn 128 or 256 (gated: 128); ctas: CTAs to launch.
+GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N,
+                                    int K, long long ldx, long long ldy, int bn, int ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return GB_ERR_SIZE;
+  const bool swiglu = mode == EPI_SWIGLU_BF16;
+  if (swiglu && bias) return GB_ERR_ARG;
+  CUtensorMap mw, mx;
+  if (!tensor_map(&mw, w, (uint64_t)N * (swiglu ? 2 : 1), (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
+  if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  if (swiglu) {
+    if (bn != 128) return GB_ERR_SIZE;
+    return launch_persistent<128, 4, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+  }
+  if (bn == 256) {
+    switch (mode) {
+      case EPI_STORE_BF16: return launch_persistent<256, 4, EPI_STORE_BF16>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+      case EPI_STORE_F32: return launch_persistent<256, 4, EPI_STORE_F32>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+      case EPI_ACCUMULATE_F32: return launch_persistent<256, 4, EPI_ACCUMULATE_F32>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+    }
+  } else if (bn == 128) {
+    switch (mode) {
+      case EPI_STORE_BF16: return launch_persistent<128, 6, EPI_STORE_BF16>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+      case EPI_STORE_F32: return launch_persistent<128, 6, EPI_STORE_F32>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+      case EPI_ACCUMULATE_F32: return launch_persistent<128, 6, EPI_ACCUMULATE_F32>(mw, mx, bias, y, M, N, K, ldy, ctas, stream);
+    }
+  } else {
+    return GB_ERR_SIZE;
+  }
+  return GB_ERR_ARG;
 }
 
 // The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator).

@@ -228,11 +228,43 @@ def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages
              bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc")
 
 
+def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=_SM_COUNT):
+    """The tensor-core product for prompts (more than 64 rows of x): one CTA per SM walks the output
+    tiles, and the epilogue of a tile runs while the next tile's MMAs fill the other accumulator
+    buffer.  Operands and modes as gemm_tc."""
+    _cuda(x, w, out, bias)
+    m, k = x.shape
+    n = w.shape[0] // 2 if swiglu else w.shape[0]
+    assert w.shape[1] == k and w.is_contiguous() and out.shape == (m, n) and out.stride(1) == 1
+    if not gemm_tc_usable(x, w):
+        raise KernelError("gemm_tc_persistent: operands must be bfloat16 with 16-byte aligned rows")
+    if swiglu:
+        if out.dtype != torch.bfloat16 or accumulate or bias is not None or w.shape[0] % 2:
+            raise KernelError("gemm_tc_persistent: the gated product writes bfloat16, without bias")
+        mode = 3
+    else:
+        mode = _TC_MODES.get((out.dtype, bool(accumulate)))
+    if mode is None:
+        raise KernelError(f"gemm_tc_persistent: cannot {'add into' if accumulate else 'store'} {out.dtype}")
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+    if bn is None:
+        bn = 128 if (swiglu or m <= 128) else 256
+    f = _fn("gemm_tc", "gb_gemm_tc_persistent",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+             c_int, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0), bn,
+             ctas, _stream()), "gemm_tc_persistent")
+
+
 def gemm_swiglu(x, w_gate_up, out):
     """out[M, N] = silu(x @ gate.T) * (x @ up.T) for w_gate_up = [gate; up] of 2N rows: one
     tensor-core kernel in bfloat16; two kernels (product, then activation) otherwise."""
     if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w_gate_up):
-        gemm_tc(x, w_gate_up, out, swiglu=True)
+        if x.shape[0] > 64:
+            gemm_tc_persistent(x, w_gate_up, out, swiglu=True)
+        else:
+            gemm_tc(x, w_gate_up, out, swiglu=True)
         return
     gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
     gemm(x, w_gate_up, gu)
@@ -409,7 +441,9 @@ def gemm(x, w, out, bias=None, accumulate=False):
     a multiple of 8), which the plain kernel takes."""
     if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w):
         m, n = x.shape[0], w.shape[0]
-        if 16 < m <= 64 and n < 128 * _SM_COUNT:
+        if m > 64:
+            gemm_tc_persistent(x, w, out, bias, accumulate)
+        elif m > 16 and n < 128 * _SM_COUNT:
             # a few dozen tokens against a matrix with few row tiles: tokens on the MMA's rows
             gemm_tc_small(x, w, out, bias, accumulate)
         else:

@@ -330,3 +330,33 @@ def test_attention_prefill_tc_against_plain(k, hd, nh, nkv, window):
         if err > worst:
             worst, where = err, (tok_seq[i], tok_pos[i])
     assert worst <= 2 ** -7, (worst, where)
+
+
+@pytest.mark.parametrize("m,n,kk,mode", [(200, 384, 1024, "bf16"), (300, 520, 256, "acc"), (515, 260, 2048, "bf16"),
+                                          (130, 128, 64, "acc"), (1000, 777, 1000, "f32")])
+def test_gemm_tc_persistent(k, m, n, kk, mode):
+    """The prompt kernel (tiles walked by one CTA per SM, two accumulator buffers), also with so few
+    CTAs that each walks many tiles."""
+    torch.manual_seed(m + 3 * n)
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(n, device="cuda") if m % 2 else None
+    ref = x.float() @ w.float().T + (b if b is not None else 0)
+    for bn in (128, 256):
+        for ctas in (148, 3):
+            if mode == "bf16":
+                out, tol, want = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16), 2 ** -8, ref
+            elif mode == "f32":
+                out, tol, want = torch.zeros(m, n, device="cuda"), 1e-5, ref
+            else:
+                out, tol, want = torch.ones(m, n, device="cuda"), 1e-5, ref + 1
+            k.gemm_tc_persistent(x, w, out, b, accumulate=(mode == "acc"), bn=bn, ctas=ctas)
+            assert (out.float() - want).abs().max().item() <= tol * want.abs().max().item() + 1e-6, (bn, ctas)
+    inter = n // 2 * 2
+    wg = (torch.randn(2 * inter, kk, device="cuda") * 0.08).bfloat16()
+    g, u = x.float() @ wg[:inter].float().T, x.float() @ wg[inter:].float().T
+    want = g / (1 + torch.exp(-g)) * u
+    out = torch.zeros(m, inter, device="cuda", dtype=torch.bfloat16)
+    k.gemm_tc_persistent(x, wg, out, swiglu=True, ctas=5)
+    assert (out.float() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item() + 1e-6
+    assert k.gemm_tc_status() == 0
