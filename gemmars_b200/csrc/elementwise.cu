@@ -126,6 +126,51 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
   const bool is_q = h < nh;
   if (is_q && !(flags & FLAG_INPLACE)) return;
   const float* w = is_q ? qw : kw;
+  if (sizeof(T) == 2 && (flags & FLAG_ROPE) && rot == hd && (hd & 3) == 0) {
+    // bfloat16, all dims rotated: each lane keeps two adjacent dims of each half (4-byte loads and
+    // stores), so the head is read once for the norm and the rotation alike
+    const int half = hd / 2;
+    const float scale = is_q ? q_scale : 1.f;
+    bf16* cdst = (!is_q && cache) ? (bf16*)kcache + kv.row(seq_slot[tok_seq[t]], pos, h - nh) : nullptr;
+    const bf16* s16 = (const bf16*)src;
+    float2 a[2], b[2];   // up to head size 256: two rounds of 64 dims per half
+    float ss = 0.f;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = 2 * lane + 64 * r;
+      if (i < half) {
+        a[r] = __bfloat1622float2(*(const __nv_bfloat162*)(s16 + i));
+        b[r] = __bfloat1622float2(*(const __nv_bfloat162*)(s16 + i + half));
+        ss += a[r].x * a[r].x + a[r].y * a[r].y + b[r].x * b[r].x + b[r].y * b[r].y;
+      }
+    }
+    float inv = 1.f;
+    if (flags & FLAG_NORM) inv = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = 2 * lane + 64 * r;
+      if (i < half) {
+        float ax = a[r].x * inv, ay = a[r].y * inv, bx = b[r].x * inv, by = b[r].y * inv;
+        if (flags & FLAG_NORM) {
+          ax *= w[i]; ay *= w[i + 1]; bx *= w[i + half]; by *= w[i + half + 1];
+        }
+        float s0, c0, s1, c1;
+        sincosf((float)pos * inv_freq[i], &s0, &c0);       // float32 product, as the reference
+        sincosf((float)pos * inv_freq[i + 1], &s1, &c1);
+        const __nv_bfloat162 ra = __floats2bfloat162_rn((ax * c0 - bx * s0) * scale, (ay * c1 - by * s1) * scale);
+        const __nv_bfloat162 rb = __floats2bfloat162_rn((bx * c0 + ax * s0) * scale, (by * c1 + ay * s1) * scale);
+        if (flags & FLAG_INPLACE) {
+          *(__nv_bfloat162*)((bf16*)src + i) = ra;
+          *(__nv_bfloat162*)((bf16*)src + i + half) = rb;
+        }
+        if (cdst) {
+          *(__nv_bfloat162*)(cdst + i) = ra;
+          *(__nv_bfloat162*)(cdst + i + half) = rb;
+        }
+      }
+    }
+    return;
+  }
   float inv = 1.f;
   if (flags & FLAG_NORM) {
     float ss = 0.f;
