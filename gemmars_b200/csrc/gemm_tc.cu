@@ -11,11 +11,12 @@
 // (lane = feature, column = token), and four warps read it back with tcgen05.ld: for one
 // token, the 32 lanes of a warp hold 32 consecutive features, so stores are coalesced.
 //
-// One kernel serves prompts (BN = 256, 128 or 64) and decoding (BN = 16..64, where the CTA
-// only streams its rows of W at memory speed).  When decoding leaves too few tiles for the
-// 148 SMs, the inner dimension is split over the CTAs of a thread-block cluster, whose partial
-// sums are added in rank order through distributed shared memory: no atomics, the same bits
-// every run.
+// Two kernels.  gemm_tc_kernel, one tile per CTA, serves decoding (BN = 16..64, where the CTA
+// only streams its rows of W at memory speed): when that leaves too few tiles for the 148 SMs,
+// the inner dimension is split over the CTAs of a thread-block cluster, whose partial sums are
+// added in rank order through distributed shared memory: no atomics, the same bits every run.
+// gemm_tc_persistent_kernel serves prompts (BN = 128 or 256): one CTA per SM walks the tiles
+// with two accumulator buffers, so a tile's epilogue runs under the next tile's MMAs.
 //
 // Warp roles (192 threads): warps 0-3 epilogue (tensor-memory lane quarter = warp id),
 // warp 4 TMA producer, warp 5 tensor-memory allocation and MMA issue.
@@ -432,165 +433,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
 }
 
-// ------------------------------------------------------------------ the kernel for few tokens
-// Decoding brings at most a few dozen tokens, and the time of a tcgen05.mma hardly shrinks
-// with its N.  So here the tokens sit on the MMA's M (128 rows, those past the batch filled
-// with zeros by TMA) and 256 output features on its N: one instruction then takes in 8 KB of W
-// instead of 4 KB, and the tensor pipe no longer limits how fast a CTA can stream its weights.
-// grid = (feature tiles of 256, 1, K splits); a cluster spans the K splits of a tile.  With
-// splits, every rank leaves its partial sums in shared memory and then adds, in rank order,
-// its own share of the tile's features over all ranks.
-constexpr int SM_TOK = 128, SM_FEAT = 256, SM_PAD = SM_FEAT + 1;
-
-template <int STAGES, int MODE>
-__global__ void __launch_bounds__(THREADS, 1)
-gemm_tc_small_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                     const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy) {
-  constexpr uint32_t A_BYTES = SM_TOK * BK * 2, B_BYTES = SM_FEAT * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = SM_FEAT;
-  constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(SM_FEAT >> 3) << 17) | ((uint32_t)(SM_TOK >> 4) << 24);
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_bar = (uint64_t*)(smem + STAGES * STAGE_BYTES);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = (uint32_t*)(tmem_bar + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * SM_FEAT;
-  const uint32_t nsplit = cluster_size(), split = cluster_rank();
-  const int kb_total = (K + BK - 1) / BK;
-  const int kb_begin = (int)((long long)kb_total * split / nsplit), kb_end = (int)((long long)kb_total * (split + 1) / nsplit);
-  const int kb_count = kb_end - kb_begin;
-
-  pdl_release_next();
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    mbar_init(tmem_bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 5) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-
-  if (warp == 4) {
-    if (lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
-      const int pre = kb_count < STAGES ? kb_count : STAGES;
-      for (int i = 0; i < pre; ++i) {   // weights first: they do not depend on the kernel before
-        mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[i]);
-      }
-      pdl_wait_prior();
-      for (int i = 0; i < pre; ++i) tma_load_2d(smem + i * STAGE_BYTES, &map_x, (kb_begin + i) * BK, 0, &full_bar[i]);
-      for (int i = pre; i < kb_count; ++i) {
-        const int s = i % STAGES;
-        if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
-          atomicCAS(&g_status, ST_OK, ST_TIMEOUT_EMPTY);
-          break;
-        }
-        uint8_t* a = smem + s * STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-        tma_load_2d(a + A_BYTES, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
-        tma_load_2d(a, &map_x, (kb_begin + i) * BK, 0, &full_bar[s]);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 5) {
-    if (lane == 0) {
-      for (int i = 0; i < kb_count; ++i) {
-        const int s = i % STAGES;
-        if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) {
-          atomicCAS(&g_status, ST_OK, ST_TIMEOUT_FULL);
-          break;
-        }
-        tc_fence_after();
-        const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
-#pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k)
-          tc_mma(tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, (i > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&empty_bar[s]);
-      }
-      tc_commit(tmem_bar);
-    }
-    __syncwarp();
-  }
-
-  // ---- epilogue: lane = token, column = feature
-  bool have_acc = false;
-  const int m = warp * 32 + lane;                 // this thread's token (warps 0-3)
-  const bool warp_has_rows = warp < 4 && warp * 32 < M;
-  if (warp < 4) {
-    if (kb_count > 0) {
-      have_acc = __all_sync(0xffffffffu, mbar_wait(tmem_bar, 0));
-      if (!have_acc && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
-    }
-    tc_fence_after();
-    pdl_wait_prior();   // y may be read (accumulate) and is written: not before the kernel before is done
-  }
-  if (nsplit > 1) {
-    float* partial = (float*)smem;                // [rows][SM_PAD], rows = min(M, 128)
-    if (warp_has_rows) {
-#pragma unroll 1
-      for (int c = 0; c < SM_FEAT; c += 16) {
-        uint32_t v[16];
-        if (have_acc) {
-          tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0u;
-        }
-        if (m < M) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) partial[m * SM_PAD + c + j] = __uint_as_float(v[j]);
-        }
-      }
-    }
-    cluster_sync();
-    if (warp < 4) {
-      const int width = SM_FEAT / (int)nsplit, f0 = (int)split * width;
-      const int rows = M < SM_TOK ? M : SM_TOK;
-      for (int idx = threadIdx.x; idx < rows * width; idx += 128) {
-        const int r = idx / width, f = f0 + idx % width, n = n0 + f;
-        float acc = 0.f;
-        for (uint32_t q = 0; q < nsplit; ++q) acc += ld_peer_f32(&partial[r * SM_PAD + f], q);
-        if (n < N) emit<MODE>(y, (size_t)r * ldy + n, acc + (bias ? bias[n] : 0.f));
-      }
-    }
-    cluster_sync();
-  } else if (warp_has_rows && have_acc) {
-#pragma unroll 1
-    for (int c = 0; c < SM_FEAT; c += 16) {
-      if (n0 + c >= N) break;
-      uint32_t v[16];
-      tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
-      tc_wait_ld();
-      if (m < M) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int n = n0 + c + j;
-          if (n < N) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + (bias ? bias[n] : 0.f));
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  __syncwarp();
-  if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
-}
-
 // ------------------------------------------------------------------ host side
 
 template <int BN, int STAGES, int MODE>
@@ -654,63 +496,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const float*
   return gb_launch_status();
 }
 
-template <int STAGES, int MODE>
-int launch_small(const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* y, int M, int N, int K,
-                 long long ldy, int splits, cudaStream_t stream) {
-  constexpr size_t SMEM = (size_t)STAGES * (SM_TOK * BK * 2 + SM_FEAT * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
-  static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
-  static_assert((size_t)64 * SM_PAD * 4 <= (size_t)STAGES * (SM_TOK * BK * 2 + SM_FEAT * BK * 2), "partial sums need the stage memory");
-  auto kernel = gemm_tc_small_kernel<STAGES, MODE>;
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
-      return (int)cudaGetLastError();
-    configured = true;
-  }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + SM_FEAT - 1) / SM_FEAT, 1, splits);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = splits;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = GB_PDL ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, kernel, mx, mw, bias, y, M, N, K, ldy);
-}
-
-template <int STAGES>
-int launch_small_mode(int mode, const CUtensorMap& mx, const CUtensorMap& mw, const float* bias, void* y, int M, int N,
-                      int K, long long ldy, int splits, cudaStream_t stream) {
-  switch (mode) {
-    case EPI_STORE_BF16: return launch_small<STAGES, EPI_STORE_BF16>(mx, mw, bias, y, M, N, K, ldy, splits, stream);
-    case EPI_STORE_F32: return launch_small<STAGES, EPI_STORE_F32>(mx, mw, bias, y, M, N, K, ldy, splits, stream);
-    case EPI_ACCUMULATE_F32: return launch_small<STAGES, EPI_ACCUMULATE_F32>(mx, mw, bias, y, M, N, K, ldy, splits, stream);
-  }
-  return GB_ERR_ARG;
-}
-
 }  // namespace
-
-// The product for at most 64 tokens (decoding): tokens on the MMA's rows, 256 features a tile.
-// Arguments as gb_gemm_tc; splits 1, 2, 4 or 8; stages 2 (two CTAs fit an SM) or 4.
-GB_EXPORT int gb_gemm_tc_small(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N, int K,
-                               long long ldx, long long ldy, int splits, int stages, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (M > 64) return GB_ERR_SIZE;
-  if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return GB_ERR_SIZE;
-  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return GB_ERR_ARG;
-  CUtensorMap mw, mx;
-  if (!tensor_map(&mw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, SM_FEAT)) return GB_ERR_ARG;
-  if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, SM_TOK)) return GB_ERR_ARG;
-  if (stages == 2) return launch_small_mode<2>(mode, mx, mw, bias, y, M, N, K, ldy, splits, stream);
-  return launch_small_mode<4>(mode, mx, mw, bias, y, M, N, K, ldy, splits, stream);
-}
 
 // x: [M, K] bfloat16, rows ldx elements apart; w: [N, K] bfloat16 contiguous; y: [M, N], rows ldy apart.
 // mode: 0 store bfloat16, 1 store float32, 2 add into float32, 3 w = [gate; up] of 2N rows and

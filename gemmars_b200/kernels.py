@@ -177,13 +177,13 @@ def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False):
         bn = 16 if m <= 16 else (32 if m <= 32 else 64)
         tiles, kb = tiles_n, -(-k // 64)
         splits = 1
-        # too few tiles to keep every SM streaming: split the inner dimension over a cluster.
-        # Only for the narrowest tile: rank 0 adds the partial sums column by column, which
-        # costs more than the split saves once a tile holds more than 16 tokens (measured).
-        # Measured with cold weights at 8 tokens: 6144 x 4096 takes 22.6 / 16.1 / 13.9 / 12.3 us with
-        # 1 / 2 / 4 / 8 splits, 4096 x 12288 takes 60 / 37 / 24 / 21 us; the gated 12288 x 4096 is best at 2.
-        enough = 150 if gated else 2 * _SM_COUNT
-        while bn == 16 and splits < 8 and tiles * splits < enough and kb // (splits * 2) >= 4:
+        # too few tiles to keep every SM streaming: split the inner dimension over a cluster, whose
+        # ranks each add a share of the tile's tokens.  Measured with cold weights (us, 1/2/4/8 splits):
+        # 8 tokens: 6144x4096 22.6/16.1/13.9/12.3, 4096x12288 60/37/24/21; gated 12288x4096 best at 2;
+        # 64 tokens: 6144x4096 24.8/21.5/17.0/19.6, 4096x4096 24/22/15/12.6, 4096x12288 63/51/32/25,
+        # gated 12288x4096 40/53/53/63.
+        enough = (150 if bn == 16 else 0) if gated else 2 * _SM_COUNT
+        while splits < 8 and tiles * splits < enough and kb // (splits * 2) >= 4:
             splits *= 2
         return bn, splits
     best, best_score = 128, -1.0
@@ -269,38 +269,6 @@ def gemm_swiglu(x, w_gate_up, out):
     gu = torch.empty((x.shape[0], w_gate_up.shape[0]), dtype=x.dtype, device=x.device)
     gemm(x, w_gate_up, gu)
     silu_mul(gu, out)
-
-
-def gemm_small_splits(n: int, k: int) -> int:
-    """K splits for the few-token kernel: enough CTAs (tiles of 256 features x splits) for the SMs,
-    while every rank keeps a few 64-wide blocks of the inner dimension."""
-    tiles, kb = -(-n // 256), -(-k // 64)
-    splits = 1
-    while splits < 8 and tiles * splits < 100 and kb // (splits * 2) >= 4:
-        splits *= 2
-    return splits
-
-
-def gemm_tc_small(x, w, out, bias=None, accumulate=False, splits=None, stages=2):
-    """The tensor-core product for at most 64 rows of x (decoding): see gemm_tc for the operands."""
-    _cuda(x, w, out, bias)
-    m, k = x.shape
-    n = w.shape[0]
-    if m > 64:
-        raise KernelError(f"gemm_tc_small takes at most 64 rows, got {m}")
-    assert w.shape[1] == k and w.is_contiguous() and out.shape == (m, n) and out.stride(1) == 1
-    if not gemm_tc_usable(x, w):
-        raise KernelError("gemm_tc_small: operands must be bfloat16 with 16-byte aligned rows")
-    mode = _TC_MODES.get((out.dtype, bool(accumulate)))
-    if mode is None:
-        raise KernelError(f"gemm_tc_small: cannot {'add into' if accumulate else 'store'} {out.dtype}")
-    if bias is not None:
-        assert bias.dtype == torch.float32 and bias.numel() == n
-    f = _fn("gemm_tc", "gb_gemm_tc_small",
-            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
-             c_int, c_void_p])
-    _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
-             splits or gemm_small_splits(n, k), stages, _stream()), "gemm_tc_small")
 
 
 def gemm_tc_status(reset: bool = True) -> int:
@@ -441,11 +409,8 @@ def gemm(x, w, out, bias=None, accumulate=False):
     a multiple of 8), which the plain kernel takes."""
     if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w):
         m, n = x.shape[0], w.shape[0]
-        if m > 64:
+        if x.shape[0] > 64:
             gemm_tc_persistent(x, w, out, bias, accumulate)
-        elif m > 16 and n < 128 * _SM_COUNT:
-            # a few dozen tokens against a matrix with few row tiles: tokens on the MMA's rows
-            gemm_tc_small(x, w, out, bias, accumulate)
         else:
             gemm_tc(x, w, out, bias, accumulate)
     else:

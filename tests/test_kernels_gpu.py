@@ -256,29 +256,6 @@ def test_attention_prefill_against_plain(k, hd, nh, nkv, window):
     assert worst <= 2 ** -7, worst
 
 
-@pytest.mark.parametrize("m,n,kk,mode,splits", [(1, 256, 64, "f32", 1), (8, 300, 1088, "bf16", 1), (5, 777, 200, "acc", 1),
-                                                 (64, 520, 4096, "bf16", 2), (33, 1000, 2048, "acc", 4),
-                                                 (64, 640, 1600, "acc", 8), (3, 256, 64, "f32", 4)])
-def test_gemm_tc_small(k, m, n, kk, mode, splits):
-    torch.manual_seed(m * 7 + n)
-    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
-    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
-    b = torch.randn(n, device="cuda") if m % 2 else None
-    ref = x.float() @ w.float().T + (b if b is not None else 0)
-    for stages in (2, 4):
-        if mode == "bf16":
-            out, tol, want = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16), 2 ** -8, ref
-        elif mode == "f32":
-            out, tol, want = torch.zeros(m, n, device="cuda"), 1e-5, ref
-        else:
-            out, tol, want = torch.ones(m, n, device="cuda"), 1e-5, ref + 1
-        k.gemm_tc_small(x, w, out, b, accumulate=(mode == "acc"), splits=splits, stages=stages)
-        assert (out.float() - want).abs().max().item() <= tol * want.abs().max().item() + 1e-6
-    assert k.gemm_tc_status() == 0
-    with pytest.raises(k.KernelError):
-        k.gemm_tc_small(torch.zeros(65, kk, device="cuda").bfloat16(), w, torch.zeros(65, n, device="cuda"))
-
-
 @pytest.mark.parametrize("m,inter,kk,bn,splits", [(1, 192, 64, None, None), (8, 160, 96, None, None), (40, 1000, 512, None, None),
                                                   (200, 384, 1024, 128, 1), (300, 520, 256, 256, 1), (64, 640, 4096, 64, 4),
                                                   (7, 12288 // 8, 4096, 16, 2)])
