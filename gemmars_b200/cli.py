@@ -92,7 +92,12 @@ def main(argv=None) -> int:
     opts.set("device", args.device)
     if args.prefill_chunk:
         opts.set("prefill_chunk", str(args.prefill_chunk))
+    if args.profile:
+        opts.set("profile", "true")
     eng = Engine.load(args.model, opts)
+    if args.profile:
+        eng._profile_from = eng.runner.steps_run
+        eng.profile_start()
     for k, v in (("max_tokens", args.max_tokens), ("temperature", args.temp), ("top_k", args.top_k),
                  ("top_p", args.top_p), ("seed", args.seed)):
         eng.set(k, v)
@@ -103,6 +108,8 @@ def main(argv=None) -> int:
         for r in eng.generate(prompts):
             print(json.dumps({"tokens": r.tokens, "reason": r.reason}))
         print(eng.stats.line(), file=sys.stderr)
+        if args.profile:
+            print(eng.profile_report(), file=sys.stderr)
         return 0
 
     by_ids = bool(args.tokens or args.tokens_file)
@@ -167,4 +174,6 @@ def main(argv=None) -> int:
     r = eng.send(ids)
     show(r.tokens)
     print(eng.stats.line(), file=sys.stderr)
+    if args.profile:
+        print(eng.profile_report(), file=sys.stderr)
     return 0

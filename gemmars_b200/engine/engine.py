@@ -114,7 +114,8 @@ class Engine:
         self.max_context = min(x for x in (options.max_context, cfg_limit, 1 << 30) if x)
         cache_tokens = options.max_tokens or min(self.max_context, 8192) * min(options.max_batch, 8)
         self.runner = Runner(model, max_tokens=cache_tokens, max_batch=options.max_batch,
-                             prefill_chunk=options.prefill_chunk or 2048, use_graphs=options.cuda_graphs)
+                             prefill_chunk=options.prefill_chunk or 2048,
+                             use_graphs=options.cuda_graphs and not options.profile)
         self.max_context = min(self.max_context, self.runner.cache.max_seq_len)
         self.stop_ids = list(model.plan.stop_ids)
         if folder is not None:
@@ -270,6 +271,16 @@ class Engine:
              "cache_pages": self.runner.cache.n_pages, "page_size": self.runner.cache.page_size,
              "stop_ids": list(self.stop_ids)}
         return d
+
+    def profile_start(self) -> None:
+        """Starts the per-kernel timing that ``profile_report`` prints (option ``profile``; decode
+        steps then run without CUDA graphs so that every launch can be timed)."""
+        from .. import kernels
+        kernels.profile_start()
+
+    def profile_report(self) -> str:
+        from .. import kernels
+        return kernels.profile_report(max(1, self.runner.steps_run - getattr(self, "_profile_from", 0)))
 
     def stats_dict(self) -> dict:
         return dataclasses.asdict(self.stats)

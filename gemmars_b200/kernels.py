@@ -54,9 +54,46 @@ def count_launches(n: int) -> None:
     _launches[0] += n
 
 
+# Per-kernel timing for --profile: an event after every launch; the time between two events is
+# put down to the later kernel (kernels of one stream run one after the other).
+_profile = {"on": False, "events": []}
+
+
+def profile_start() -> None:
+    """Starts collecting one CUDA event per launch (use without CUDA graphs)."""
+    _profile["on"], _profile["events"] = True, []
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    _profile["events"].append(("start", ev))
+
+
+def profile_report(steps: int = 1) -> str:
+    """The time per kernel name since profile_start, in the manner of the reference's --profile
+    (src/prof.rs:51-83): ms a step, calls a step, us a call, share."""
+    _profile["on"] = False
+    torch.cuda.synchronize()
+    ev = _profile["events"]
+    totals = {}
+    for (_, a), (name, b) in zip(ev, ev[1:]):
+        t = totals.setdefault(name, [0, 0.0])
+        t[0] += 1
+        t[1] += a.elapsed_time(b)
+    whole = sum(t[1] for t in totals.values()) or 1.0
+    lines = [f"{'kernel':28s} {'ms/step':>9s} {'calls/step':>11s} {'us/call':>9s} {'share':>7s}"]
+    for name, (calls, ms) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
+        lines.append(f"{name:28s} {ms / steps:9.3f} {calls / steps:11.1f} {ms * 1e3 / calls:9.1f} {100 * ms / whole:6.1f}%")
+    lines.append(f"{'total':28s} {whole / steps:9.3f}")
+    _profile["events"] = []
+    return "\n".join(lines)
+
+
 def _check(code: int, what: str):
     if code == 0:
         _launches[0] += 1
+        if _profile["on"]:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            _profile["events"].append((what, ev))
         return
     if code < 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, 'refused')} (code {code})")

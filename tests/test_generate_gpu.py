@@ -142,6 +142,11 @@ def test_command_line(model_folders, tmp_path):
     assert p.returncode == 0, p.stderr[-2000:]
     got = np.fromfile(dump, dtype="<f4")
     assert np.abs(got - plain.forward(pcfg, w, prompt)[-1]).max() < 2e-5
+    p = subprocess.run(base + ["--tokens", ",".join(map(str, prompt)), "-n", "6", "--profile"], capture_output=True,
+                       text=True, cwd=ROOT, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [int(x) for x in p.stdout.strip().split(",")] == want
+    assert "ms/step" in p.stderr and "attention_ref" in p.stderr and "gemm_ref" in p.stderr
     batch = tmp_path / "batch.txt"
     batch.write_text("1 2 3\n9,8,7,6,5\n")
     p = subprocess.run(base + ["--batch-file", str(batch), "-n", "4"], capture_output=True, text=True, cwd=ROOT,
