@@ -89,11 +89,22 @@ attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
 #pragma unroll
   for (int d = 0; d < HD / 8; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
 
+  // the page of a block is looked up one block ahead, so that the lookup's round trip to memory
+  // runs under the block before and not in front of this block's loads
+  const int* table_row = kv.page_table + (size_t)slot * kv.table_width;
+  int next_page = b_begin + warp < b_end ? table_row[((b_begin + warp) * KEYS / kv.page_size) % kv.table_width] : 0;
   for (int blk = b_begin + warp; blk < b_end; blk += WARPS) {
     const int key0 = blk * KEYS;
-    const int page = kv.page_table[(size_t)slot * kv.table_width + (key0 / kv.page_size) % kv.table_width];
+    const int page = next_page;
+    if (blk + WARPS < b_end) next_page = table_row[((blk + WARPS) * KEYS / kv.page_size) % kv.table_width];
     const size_t page_base = ((size_t)page * kv.num_kv_heads + kvh) * kv.page_size * HD;
     const int in_page = key0 % kv.page_size;
+    // ---- the block's values are asked for now, before the scores are computed: their loads are
+    // in flight during the first product and the softmax (the kernel lives on loads in flight)
+    const bf16* vbase = vcache + page_base + in_page + 8 * c;
+    uint4 vv[HD / 8];
+#pragma unroll
+    for (int d = 0; d < HD / 8; ++d) vv[d] = *(const uint4*)(vbase + (size_t)(d * 8 + g) * kv.page_size);
     // ---- scores: group j of 8 MMA columns; column n holds key 8 (n / 2) + 2 j + (n % 2)
     float s[4][4];
 #pragma unroll
@@ -143,10 +154,9 @@ attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
     l0 = l0 * alpha0 + sum0;
     l1 = l1 * alpha1 + sum1;
     // ---- o = o * alpha + p . V; values are [dim][position] inside the page
-    const bf16* vbase = vcache + page_base + in_page + 8 * c;
 #pragma unroll
     for (int d = 0; d < HD / 8; ++d) {
-      const uint4 v4 = *(const uint4*)(vbase + (size_t)(d * 8 + g) * kv.page_size);
+      const uint4 v4 = vv[d];
       o[d][0] *= alpha0; o[d][1] *= alpha0; o[d][2] *= alpha1; o[d][3] *= alpha1;
       mma16816(o[d], p[0][0], UPPER ? p[0][1] : 0u, p[1][0], UPPER ? p[1][1] : 0u, v4.x, v4.y);
       mma16816(o[d], p[2][0], UPPER ? p[2][1] : 0u, p[3][0], UPPER ? p[3][1] : 0u, v4.z, v4.w);
