@@ -52,15 +52,28 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   if ((n & 3) == 0) {
     const float4* row4 = (const float4*)row;
     const float4* w4 = (const float4*)w;
+    constexpr int KEEP = 4;            // float4s a thread keeps in registers between the two passes
+    const bool keep = n / 4 <= KEEP * (int)blockDim.x;
+    float4 held[KEEP];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
-      const float4 v = row4[i];
-      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (keep) {
+#pragma unroll
+      for (int u = 0; u < KEEP; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        held[u] = i < n / 4 ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < KEEP; ++u) ss += held[u].x * held[u].x + held[u].y * held[u].y + held[u].z * held[u].z + held[u].w * held[u].w;
+    } else {
+      for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
+        const float4 v = row4[i];
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-    for (int i = threadIdx.x; i < n / 4; i += blockDim.x) {
-      const float4 v = row4[i], g = w4[i];
+    for (int u = 0, i = threadIdx.x; i < n / 4; i += blockDim.x, ++u) {
+      const float4 v = keep ? held[u < KEEP ? u : 0] : row4[i], g = w4[i];
       const float a = v.x * inv * g.x, b = v.y * inv * g.y, c = v.z * inv * g.z, d = v.w * inv * g.w;
       if (sizeof(T) == 4) {
         ((float4*)o)[i] = make_float4(a, b, c, d);
@@ -81,7 +94,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
 GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
                          int n, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const int threads = n >= 4096 ? 512 : (n >= 1024 ? 256 : 128);
+  const int threads = n >= 1024 ? 256 : 128;
   if (out_dtype == GB_F32)
     gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps);
   else if (out_dtype == GB_BF16)
@@ -98,27 +111,23 @@ GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtyp
 //   k heads: optional RMSNorm (weight kw), optional rotation; written back in place and, with
 //            FLAG_CACHE, into the paged key cache.
 //   v heads: with FLAG_CACHE copied into the paged value cache (transposed inside the page).
-enum { FLAG_NORM = 1, FLAG_ROPE = 2, FLAG_CACHE = 4, FLAG_INPLACE = 8 };
+enum { FLAG_NORM = 1, FLAG_ROPE = 2, FLAG_CACHE = 4, FLAG_INPLACE = 8, FLAG_V_TILED = 16 };
 
+// One head of one token, by one warp.  cs / sn: cos and sin of the token's angles (rot / 2 each).
 template <typename T>
-__global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int nh, int nkv, int hd, int rot,
-                                            const float* __restrict__ qw, const float* __restrict__ kw, float eps,
-                                            const float* __restrict__ inv_freq, float q_scale,
-                                            const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                                            const int* __restrict__ seq_slot, PagedKV kv, T* __restrict__ kcache,
-                                            T* __restrict__ vcache, int flags) {
-  pdl_release_next();
-  pdl_wait_prior();
+__device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, int t, int h, int pos, int nh, int nkv, int hd,
+                                                         int rot, const float* __restrict__ qw,
+                                                         const float* __restrict__ kw, float eps,
+                                                         const float* __restrict__ cs, const float* __restrict__ sn,
+                                                         float q_scale, const int* __restrict__ tok_seq,
+                                                         const int* __restrict__ seq_slot, const PagedKV& kv,
+                                                         T* __restrict__ kcache, T* __restrict__ vcache, int flags) {
   const int lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
-  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (gw >= (long long)ntok * heads) return;
-  const int t = (int)(gw / heads), h = (int)(gw % heads);
   T* src = qkv + ((size_t)t * heads + h) * hd;
-  const int pos = tok_pos[t];
   const bool cache = flags & FLAG_CACHE;
   if (h >= nh + nkv) {  // value head
-    if (!cache) return;
+    if (!cache || (flags & FLAG_V_TILED)) return;   // tiled: value_cache_tile_kernel writes the values
     T* dst = vcache + kv.vcol(seq_slot[tok_seq[t]], pos, h - nh - nkv);
     for (int i = lane; i < hd; i += 32) dst[(size_t)i * kv.page_size] = src[i];
     return;
@@ -154,9 +163,7 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
         if (flags & FLAG_NORM) {
           ax *= w[i]; ay *= w[i + 1]; bx *= w[i + half]; by *= w[i + half + 1];
         }
-        float s0, c0, s1, c1;
-        sincosf((float)pos * inv_freq[i], &s0, &c0);       // float32 product, as the reference
-        sincosf((float)pos * inv_freq[i + 1], &s1, &c1);
+        const float s0 = sn[i], c0 = cs[i], s1 = sn[i + 1], c1 = cs[i + 1];
         const __nv_bfloat162 ra = __floats2bfloat162_rn((ax * c0 - bx * s0) * scale, (ay * c1 - by * s1) * scale);
         const __nv_bfloat162 rb = __floats2bfloat162_rn((bx * c0 + ax * s0) * scale, (by * c1 + ay * s1) * scale);
         if (flags & FLAG_INPLACE) {
@@ -192,9 +199,7 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
       a *= w[i];
       b *= w[i + half];
     }
-    const float ang = (float)pos * inv_freq[i];  // float32 product, as the reference
-    float s, c;
-    sincosf(ang, &s, &c);
+    const float s = sn[i], c = cs[i];
     const T ra = from_f32<T>((a * c - b * s) * scale), rb = from_f32<T>((b * c + a * s) * scale);
     if (inplace) {
       src[i] = ra;
@@ -214,6 +219,62 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
   }
 }
 
+// One CTA per token: the token's rot / 2 angles (float32(position) * inv_freq, as the reference)
+// and their cos and sin are computed once into shared memory, then the warps take the heads in turn.
+template <typename T>
+__global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int nh, int nkv, int hd, int rot,
+                                            const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                            const float* __restrict__ inv_freq, float q_scale,
+                                            const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                            const int* __restrict__ seq_slot, PagedKV kv, T* __restrict__ kcache,
+                                            T* __restrict__ vcache, int flags) {
+  extern __shared__ float trig[];   // cos [rot / 2], sin [rot / 2]
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  const int half = (flags & FLAG_ROPE) ? rot / 2 : 0;
+  float* cs = trig;
+  float* sn = trig + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+  __syncthreads();
+  const int heads = nh + 2 * nkv;
+  for (int h = threadIdx.x >> 5; h < heads; h += blockDim.x >> 5)
+    head_norm_rope_cache_one<T>(qkv, t, h, pos, nh, nkv, hd, rot, qw, kw, eps, cs, sn, q_scale, tok_seq, seq_slot, kv, kcache,
+                                vcache, flags);
+}
+
+// The values of 32 consecutive packed tokens for one kv head, written into the cache through a
+// shared-memory transpose: rows are read 16 bytes at a time, and each store instruction of a warp
+// then covers one dim of 32 tokens, which are consecutive positions of a page for a prompt (64
+// contiguous bytes instead of 32 scattered two-byte stores).
+template <typename T>
+__global__ void __launch_bounds__(128) value_cache_tile_kernel(const T* __restrict__ qkv, int ntok, int nh, int nkv, int hd,
+                                                               const int* __restrict__ tok_pos,
+                                                               const int* __restrict__ tok_seq,
+                                                               const int* __restrict__ seq_slot, PagedKV kv,
+                                                               T* __restrict__ vcache) {
+  extern __shared__ unsigned char tile_raw[];
+  T* tile = (T*)tile_raw;                 // [32][hd + 2]
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t0 = blockIdx.x * 32, kvh = blockIdx.y, pitch = hd + 2;
+  const int heads = nh + 2 * nkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int r = warp; r < 32; r += 4) {
+    const int t = t0 + r;
+    if (t < ntok) {
+      const T* src = qkv + ((size_t)t * heads + nh + nkv + kvh) * hd;
+      for (int i = lane; i < hd; i += 32) tile[r * pitch + i] = src[i];
+    }
+  }
+  __syncthreads();
+  const int t = t0 + lane;
+  if (t >= ntok) return;
+  T* dst = vcache + kv.vcol(seq_slot[tok_seq[t]], tok_pos[t], kvh);
+  for (int d = warp; d < hd; d += 4) dst[(size_t)d * kv.page_size] = tile[lane * pitch + d];
+}
+
 GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, int nkv, int hd, int rot,
                                       const float* qw, const float* kw, float eps, const float* inv_freq,
                                       float q_scale, const int* tok_pos, const int* tok_seq, const int* seq_slot,
@@ -224,19 +285,29 @@ GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, in
   if ((flags & FLAG_NORM) && (!qw || !kw)) return GB_ERR_ARG;
   if ((flags & FLAG_ROPE) && !inv_freq) return GB_ERR_ARG;
   PagedKV kv{page_table, table_width, page_size, nkv, hd};
-  const long long warps = (long long)ntok * (nh + 2 * nkv);
-  const int wpb = 4;
-  const unsigned grid = (unsigned)((warps + wpb - 1) / wpb);
+  const bool v_tiled = (flags & FLAG_CACHE) && nkv > 0 && ntok >= 64;   // prompts: values through the transposing kernel
+  if (v_tiled) flags |= FLAG_V_TILED;
+  const int threads = (nh + 2 * nkv) >= 8 ? 256 : 32 * (nh + 2 * nkv);
+  const size_t trig_bytes = (size_t)rot * sizeof(float);
   if (dtype == GB_F32)
-    gb_launch(head_norm_rope_cache_kernel<float>, grid, wpb * 32, 0, stream, 
+    gb_launch(head_norm_rope_cache_kernel<float>, ntok, threads, trig_bytes, stream,
         (float*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
         (float*)kcache, (float*)vcache, flags);
   else if (dtype == GB_BF16)
-    gb_launch(head_norm_rope_cache_kernel<bf16>, grid, wpb * 32, 0, stream, 
+    gb_launch(head_norm_rope_cache_kernel<bf16>, ntok, threads, trig_bytes, stream,
         (bf16*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
         (bf16*)kcache, (bf16*)vcache, flags);
   else
     return GB_ERR_DTYPE;
+  int rc = gb_launch_status();
+  if (rc != 0 || !v_tiled) return rc;
+  dim3 vgrid((ntok + 31) / 32, nkv);
+  if (dtype == GB_F32)
+    gb_launch(value_cache_tile_kernel<float>, vgrid, 128, (size_t)32 * (hd + 2) * 4, stream, (const float*)qkv, ntok, nh, nkv,
+              hd, tok_pos, tok_seq, seq_slot, kv, (float*)vcache);
+  else
+    gb_launch(value_cache_tile_kernel<bf16>, vgrid, 128, (size_t)32 * (hd + 2) * 2, stream, (const bf16*)qkv, ntok, nh, nkv,
+              hd, tok_pos, tok_seq, seq_slot, kv, (bf16*)vcache);
   return gb_launch_status();
 }
 

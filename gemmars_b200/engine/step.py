@@ -14,8 +14,9 @@ that start together and the requested rows are this engine's own.
 from __future__ import annotations
 
 import dataclasses
-from typing import List, Optional, Sequence, Tuple
+from typing import Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.pool import CacheError, SequenceCache
@@ -34,6 +35,33 @@ class StepItem:
     want: Sequence[int] = ()      # places among ``tokens`` whose logits are asked for
 
 
+class _PinnedRing:
+    """A few pinned host buffers used in turn for the step's index block; a buffer is written
+    again only after the copy that last read it has finished.  They are allocated once, for the
+    largest step, since pinning memory takes about a millisecond."""
+
+    def __init__(self, capacity: int, n: int = 4):
+        self.bufs = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(n)]
+        self.views = [b.numpy() for b in self.bufs]
+        self.events = [None] * n
+        self.turn = 0
+
+    def stage(self, values: np.ndarray, device) -> torch.Tensor:
+        i = self.turn
+        self.turn = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        if self.bufs[i].numel() < values.size:
+            self.bufs[i] = torch.empty(2 * values.size, dtype=torch.int32).pin_memory()
+            self.views[i] = self.bufs[i].numpy()
+        self.views[i][:values.size] = values
+        dev = self.bufs[i][:values.size].to(device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+        return dev
+
+
 class Runner:
     """A model with its cache: opens and closes sequences and runs steps."""
 
@@ -49,8 +77,8 @@ class Runner:
         self.use_graphs = use_graphs
         self._graphs = {}
         self._pool = None
+        self._ring = _PinnedRing(4 * self.max_step_tokens + 8 * self.cache.n_slots + 64) if self.device.type == "cuda" else None
         self.steps_run = 0
-        self.launch_count = 0
 
     def _graph_pool(self):
         if self._pool is None:
@@ -73,23 +101,26 @@ class Runner:
         items and of each item's ``want`` (None when nothing is wanted)."""
         items = list(items)
         seen = set()
+        toks = []
         for it in items:
             if it.slot in seen:
                 raise StepError(f"slot {it.slot} appears twice in one step")
             seen.add(it.slot)
             if it.slot not in self.cache.lengths:
                 raise StepError(f"slot {it.slot} is not open")
-            if len(it.tokens) == 0:
+            t = np.asarray(it.tokens, dtype=np.int64).reshape(-1)
+            if t.size == 0:
                 raise StepError(f"slot {it.slot} brings no token")
-            for t in it.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise StepError(f"token id {t} is outside the vocabulary (0..{self.vocab_size - 1})")
+            if t.min() < 0 or t.max() >= self.vocab_size:
+                bad = int(t[(t < 0) | (t >= self.vocab_size)][0])
+                raise StepError(f"token id {bad} is outside the vocabulary (0..{self.vocab_size - 1})")
             for w in it.want:
-                if not 0 <= int(w) < len(it.tokens):
-                    raise StepError(f"wanted place {w} is outside the {len(it.tokens)} tokens of slot {it.slot}")
-        if not self.cache.can_extend([(it.slot, len(it.tokens)) for it in items]):
+                if not 0 <= int(w) < t.size:
+                    raise StepError(f"wanted place {w} is outside the {t.size} tokens of slot {it.slot}")
+            toks.append(t)
+        if not self.cache.can_extend([(it.slot, t.size) for it, t in zip(items, toks)]):
             raise CacheError("the step does not fit in the cache "
-                             f"({sum(len(it.tokens) for it in items)} new tokens; "
+                             f"({sum(t.size for t in toks)} new tokens; "
                              f"longest sequence allowed {self.cache.max_seq_len})")
         n_want = sum(len(it.want) for it in items)
         out = (torch.empty((n_want, self.vocab_size), dtype=torch.float32, device=self.device)
@@ -103,8 +134,8 @@ class Runner:
         while True:
             # one sub-step: up to prefill_chunk tokens of each unfinished sequence, within the budget
             budget, part = self.max_step_tokens, []
-            for i, it in enumerate(items):
-                left = len(it.tokens) - done[i]
+            for i, t in enumerate(toks):
+                left = t.size - done[i]
                 if left <= 0 or budget <= 0:
                     continue
                 n = min(left, self.prefill_chunk, budget)
@@ -112,45 +143,49 @@ class Runner:
                 budget -= n
             if not part:
                 break
-            self._run(items, part, out, out_base)
+            self._run(items, toks, part, out, out_base)
             for i, _, n in part:
                 done[i] += n
         self.steps_run += 1
         return out
 
-    def _run(self, items, part, out, out_base):
+    def _run(self, items, toks, part, out, out_base):
         cache = self.cache
-        tokens, tok_pos, tok_seq, seq_slot, seq_start, seq_len, cu = [], [], [], [], [], [], [0]
+        b = len(part)
+        slots = np.empty(b, dtype=np.int64)
+        starts = np.empty(b, dtype=np.int64)
+        lens = np.empty(b, dtype=np.int64)
         rows, dest = [], []
-        max_total = 0
-        for b, (i, off, n) in enumerate(part):
+        base = 0
+        for k, (i, off, n) in enumerate(part):
             it = items[i]
-            start = cache.extend(it.slot, n)
-            tokens.extend(int(t) for t in it.tokens[off:off + n])
-            tok_pos.extend(range(start, start + n))
-            tok_seq.extend([b] * n)
-            seq_slot.append(it.slot)
-            seq_start.append(start)
-            seq_len.append(n)
+            slots[k], starts[k], lens[k] = it.slot, cache.extend(it.slot, n), n
             for j, w in enumerate(it.want):
                 if off <= w < off + n:
-                    rows.append(cu[-1] + (w - off))
+                    rows.append(base + (w - off))
                     dest.append(out_base[i] + j)
-            cu.append(cu[-1] + n)
-            max_total = max(max_total, start + n)
+            base += n
         cache.sync()
-        t, b = len(tokens), len(part)
+        t = base
+        max_total = int((starts + lens).max())
+        contiguous = bool(dest) and dest == list(range(dest[0], dest[0] + len(dest)))
         if self.use_graphs and t == b and len(rows) == b and rows == list(range(b)):
             # every sequence brings one token and wants its logits: replay the captured step
-            logits = self._decode_graph(tokens, tok_pos, seq_slot, seq_start, max_total)
-            if dest == list(range(dest[0], dest[0] + b)):
+            tokens = np.fromiter((toks[i][off] for i, off, _ in part), dtype=np.int64, count=b)
+            logits = self._decode_graph(tokens, starts, slots, max_total)
+            if contiguous:
                 out[dest[0]:dest[0] + b].copy_(logits)
             else:
                 out[torch.tensor(dest, device=self.device)] = logits
             return
-        host = torch.tensor(tokens + tok_pos + tok_seq + seq_slot + seq_start + seq_len + cu + rows,
-                            dtype=torch.int32).pin_memory()
-        dev = host.to(self.device, non_blocking=True)
+        cu = np.zeros(b + 1, dtype=np.int64)
+        np.cumsum(lens, out=cu[1:])
+        tok_seq = np.repeat(np.arange(b), lens)
+        tok_pos = np.arange(t) - cu[tok_seq] + starts[tok_seq]
+        tokens = np.concatenate([toks[i][off:off + n] for i, off, n in part])
+        block = np.concatenate([tokens, tok_pos, tok_seq, slots, starts, lens, cu,
+                                np.asarray(rows, dtype=np.int64)]).astype(np.int32)
+        dev = self._ring.stage(block, self.device)
         o = 0
 
         def take(n):
@@ -164,18 +199,18 @@ class Runner:
         ctx = StepContext(
             compute=self.model.compute, act_dtype=self.model.act_dtype, device=self.device, n_tokens=t, n_seqs=b,
             tok_pos=d_pos, tok_seq=d_seq, seq_slot=d_slot, seq_start=d_start, seq_len=d_len, cu_seqlens=d_cu,
-            is_decode=all(n == 1 for n in seq_len), max_new=max(seq_len), max_total=max_total, cache=cache,
+            is_decode=bool((lens == 1).all()), max_new=int(lens.max()), max_total=max_total, cache=cache,
             page_size=cache.page_size)
         x = self.model.forward(ctx, d_tokens)
         if rows:
             logits = self.model.logits(ctx, x, d_rows)
-            if dest == list(range(dest[0], dest[0] + len(dest))):
+            if contiguous:
                 out[dest[0]:dest[0] + len(dest)].copy_(logits)
             else:
                 out[torch.tensor(dest, device=self.device)] = logits
 
     # ---- decode steps replayed from CUDA graphs
-    def _decode_graph(self, tokens, tok_pos, seq_slot, seq_start, max_total):
+    def _decode_graph(self, tokens, starts, slots, max_total):
         """One token per sequence through a captured graph.  The batch is padded to a power of
         two with rows that belong to no sequence: they use the page table's spare row, write into
         page 0 and read nothing that a real row reads, so they change no result."""
@@ -190,7 +225,7 @@ class Runner:
         g = self._graphs.get(key)
         if g is None:
             g = self._graphs[key] = _DecodeGraph(self, bp, len_bucket)
-        return g.run(tokens, tok_pos, seq_slot, seq_start)[:b]
+        return g.run(tokens, starts, slots)[:b]
 
 
 class _DecodeGraph:
@@ -207,6 +242,7 @@ class _DecodeGraph:
         self.n = 8 * bp + 1
         self.meta = torch.zeros(self.n, dtype=torch.int32, device=dev)
         self.host = [torch.zeros(self.n, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
+        self.host_np = [h.numpy() for h in self.host]
         self.events = [None] * self.RING
         self.turn = 0
         m, o = self.meta, 0
@@ -220,14 +256,14 @@ class _DecodeGraph:
         self.d_tokens, self.d_pos, self.d_seq = take(bp), take(bp), take(bp)
         self.d_slot, self.d_start, self.d_len, self.d_cu, self.d_rows = take(bp), take(bp), take(bp), take(bp + 1), take(bp)
         pad_slot = runner.cache.n_slots
-        fixed = torch.zeros(self.n, dtype=torch.int32)
-        fixed[2 * bp:3 * bp] = torch.arange(bp)            # tok_seq
+        fixed = np.zeros(self.n, dtype=np.int32)
+        fixed[2 * bp:3 * bp] = np.arange(bp)               # tok_seq
         fixed[3 * bp:4 * bp] = pad_slot                     # seq_slot of padding rows
         fixed[5 * bp:6 * bp] = 1                            # seq_len
-        fixed[6 * bp:7 * bp + 1] = torch.arange(bp + 1)     # cu_seqlens
-        fixed[7 * bp + 1:8 * bp + 1] = torch.arange(bp)     # wanted rows
+        fixed[6 * bp:7 * bp + 1] = np.arange(bp + 1)        # cu_seqlens
+        fixed[7 * bp + 1:8 * bp + 1] = np.arange(bp)        # wanted rows
         self.fixed = fixed
-        self.meta.copy_(fixed)
+        self.meta.copy_(torch.from_numpy(fixed))
         model = runner.model
         self.ctx = StepContext(
             compute=model.compute, act_dtype=model.act_dtype, device=dev, n_tokens=bp, n_seqs=bp,
@@ -249,20 +285,20 @@ class _DecodeGraph:
         x = model.forward(self.ctx, self.d_tokens)
         return model.logits(self.ctx, x, self.d_rows)
 
-    def run(self, tokens, tok_pos, seq_slot, seq_start):
+    def run(self, tokens, starts, slots):
         from .. import kernels
         b, bp = len(tokens), self.bp
         i = self.turn
         self.turn = (i + 1) % self.RING
         if self.events[i] is not None:
             self.events[i].synchronize()       # the copy that last read this host buffer is done
-        h = self.host[i]
-        h.copy_(self.fixed)
-        h[0:b] = torch.tensor(tokens, dtype=torch.int32)
-        h[bp:bp + b] = torch.tensor(tok_pos, dtype=torch.int32)
-        h[3 * bp:3 * bp + b] = torch.tensor(seq_slot, dtype=torch.int32)
-        h[4 * bp:4 * bp + b] = torch.tensor(seq_start, dtype=torch.int32)
-        self.meta.copy_(h, non_blocking=True)
+        h = self.host_np[i]
+        h[:] = self.fixed
+        h[0:b] = tokens
+        h[bp:bp + b] = starts                  # the token's position is the length before the step
+        h[3 * bp:3 * bp + b] = slots
+        h[4 * bp:4 * bp + b] = starts
+        self.meta.copy_(self.host[i], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev

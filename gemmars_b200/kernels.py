@@ -166,6 +166,8 @@ def head_norm_rope_cache(qkv, nh, nkv, hd, rot, q_weight, k_weight, eps, inv_fre
              eps, _ptr(inv_freq), q_scale, tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(),
              _ptr(page_table), page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache),
              _ptr(vcache), flags, _stream()), "head_norm_rope_cache")
+    if (flags & FLAG_CACHE) and nkv > 0 and qkv.shape[0] >= 64:
+        count_launches(1)   # prompts: the values go through a second, transposing kernel
 
 
 def silu_mul(gu: torch.Tensor, out: torch.Tensor):
