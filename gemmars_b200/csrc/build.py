@@ -74,7 +74,7 @@ def library_path(unit: str, defines: Sequence[Tuple[str, object]] = ()) -> Tuple
     if not os.path.exists(src):
         raise KernelBuildError(f"no CUDA source {src}")
     flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in defines]
-    # further defines for every unit, e.g. GEMMARS_B200_DEFINES="GB_PDL=0" to launch plainly
+    # further defines for every unit (experiments), e.g. GEMMARS_B200_DEFINES="GB_DECODE_MIN_CTAS=2"
     flags += [f"-D{d.strip()}" for d in os.environ.get("GEMMARS_B200_DEFINES", "").split(",") if d.strip()]
     h = hashlib.sha256()
     with open(src, "rb") as f:
@@ -131,13 +131,34 @@ def load(unit: str, defines: Sequence[Tuple[str, object]] = ()) -> ctypes.CDLL:
         return lib
 
 
+def loaded() -> Dict[str, ctypes.CDLL]:
+    """The libraries loaded so far, by path."""
+    with _lock:
+        return dict(_loaded)
+
+
+PDL_DEFINE = ("GB_PDL", 1)
+_pdl = [False]
+
+
+def set_pdl(on: bool) -> None:
+    """Whether the next launches use the units' builds with programmatic dependent launch (a kernel
+    may start under the one before it).  The engine turns it on for prompt steps."""
+    _pdl[0] = bool(on)
+
+
+def pdl() -> bool:
+    return _pdl[0]
+
+
 def ensure(units: Iterable[Tuple[str, Sequence[Tuple[str, object]]]], jobs: Optional[int] = None) -> None:
     """Compiles, in parallel, those of ``units`` ((unit, defines) pairs) that are not built yet."""
     todo = []
     for unit, defines in units:
-        path, flags = library_path(unit, tuple(defines))
-        if not os.path.exists(path) and (unit, path) not in [(u, p) for u, p, _ in todo]:
-            todo.append((unit, path, flags))
+        for variant in (tuple(defines), tuple(defines) + (PDL_DEFINE,)):   # both builds: see set_pdl
+            path, flags = library_path(unit, variant)
+            if not os.path.exists(path) and (unit, path) not in [(u, p) for u, p, _ in todo]:
+                todo.append((unit, path, flags))
     if not todo:
         return
     with ThreadPoolExecutor(max_workers=jobs or min(len(todo), os.cpu_count() or 4)) as ex:

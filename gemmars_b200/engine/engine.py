@@ -18,6 +18,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..config.base import load_stop_ids
 from ..sampling.sampler import BatchSampler, SamplingParams
 from .generate import CANCELLED, LENGTH, STOP, Generated, GenerationLoop, Request
@@ -187,6 +188,7 @@ class Engine:
                         dataclasses.replace(base, seed=base.seed + i)) for i, p in enumerate(prompts)]
         loop = self._loop()
         results = loop.run(reqs, on_token)
+        kernels.check_status()
         self.stats = Stats(sum(len(p) for p in prompts), loop.decode_tokens, loop.prefill_secs, loop.decode_secs,
                            loop.decode_steps)
         return results
@@ -201,6 +203,7 @@ class Engine:
 
     def _timed(self, loop, reqs, cb):
         res = loop.run(reqs, cb)
+        kernels.check_status()
         self.stats = Stats(sum(len(r.prompt) for r in reqs), loop.decode_tokens, loop.prefill_secs,
                            loop.decode_secs, loop.decode_steps)
         return res
@@ -239,6 +242,7 @@ class Engine:
             logits = r.step([StepItem(self._conv_slot, [tok], [0])])
             steps += 1
         torch.cuda.synchronize(r.device)
+        kernels.check_status()
         self.stats = Stats(len(feed), len(out), t1 - t0, time.perf_counter() - t1, steps)
         return Generated(out, reason, len(feed), steps)
 

@@ -20,6 +20,7 @@ import numpy as np
 import torch
 
 from ..cache.pool import CacheError, SequenceCache
+from ..csrc import build
 from ..parts.base import StepContext
 from .model import DecoderModel
 
@@ -201,7 +202,12 @@ class Runner:
             tok_pos=d_pos, tok_seq=d_seq, seq_slot=d_slot, seq_start=d_start, seq_len=d_len, cu_seqlens=d_cu,
             is_decode=bool((lens == 1).all()), max_new=int(lens.max()), max_total=max_total, cache=cache,
             page_size=cache.page_size)
-        x = self.model.forward(ctx, d_tokens)
+        # prompts run kernel by kernel: let each start under the one before (closes the launch gaps)
+        build.set_pdl(t > b)
+        try:
+            x = self.model.forward(ctx, d_tokens)
+        finally:
+            build.set_pdl(False)
         if rows:
             logits = self.model.logits(ctx, x, d_rows)
             if contiguous:
@@ -270,7 +276,8 @@ class _DecodeGraph:
             tok_pos=self.d_pos, tok_seq=self.d_seq, seq_slot=self.d_slot, seq_start=self.d_start, seq_len=self.d_len,
             cu_seqlens=self.d_cu, is_decode=True, max_new=1, max_total=len_bucket, cache=runner.cache,
             page_size=runner.cache.page_size)
-        # once eagerly (loads the kernels, warms the allocator), then captured
+        # once eagerly (loads the kernels, warms the allocator), then captured; plain launches
+        build.set_pdl(False)
         torch.cuda.synchronize(dev)
         self._forward()
         torch.cuda.synchronize(dev)

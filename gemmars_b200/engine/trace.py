@@ -23,6 +23,7 @@ import sys
 
 import torch
 
+from .. import kernels
 from .model import build_model
 from .step import Runner, StepItem
 
@@ -55,6 +56,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
             logits = runner.step(items)
             if logits is not None:
                 data = logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False)
+                kernels.check_status()
                 with open(os.path.join(out_dir, f"{rec['step']}.f32"), "wb") as f:
                     f.write(data.tobytes())
         for rid in rec.get("end", []):

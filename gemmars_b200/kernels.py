@@ -111,6 +111,8 @@ _sigs = {}
 
 
 def _fn(unit: str, name: str, argtypes, defines=()):
+    if build.pdl():
+        defines = tuple(defines) + (build.PDL_DEFINE,)
     key = (unit, name, tuple(defines))
     f = _sigs.get(key)
     if f is None:
@@ -310,12 +312,38 @@ def gemm_swiglu(x, w_gate_up, out):
     silu_mul(gu, out)
 
 
+_STATUS_ENTRIES = ("gb_gemm_tc_status", "gb_attention_prefill_tc_status")
+
+
+def _status(entry: str, reset: bool) -> int:
+    """First non-zero status word among the loaded libraries that export ``entry`` (every build of
+    a unit keeps a word of its own)."""
+    first = 0
+    for lib in build.loaded().values():
+        try:
+            f = getattr(lib, entry)
+        except AttributeError:
+            continue
+        f.argtypes, f.restype = [c_int], c_int
+        v = f(1 if reset else 0)
+        first = first or v
+    return first
+
+
 def gemm_tc_status(reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in a gemm_tc launch (synchronizes)."""
-    lib = build.load("gemm_tc")
-    lib.gb_gemm_tc_status.argtypes = [c_int]
-    lib.gb_gemm_tc_status.restype = c_int
-    return lib.gb_gemm_tc_status(1 if reset else 0)
+    return _status("gb_gemm_tc_status", reset)
+
+
+def check_status() -> None:
+    """Raises if a bounded wait ran out in any tensor-core kernel since the last check: such a
+    kernel gives up and leaves its output unfinished, so what was computed since must not be used.
+    Synchronizes; the engine calls it before results leave it."""
+    for entry in _STATUS_ENTRIES:
+        v = _status(entry, True)
+        if v:
+            raise KernelError(f"{entry[3:-7]}: a bounded wait ran out on the device (code {v}); "
+                              "the results computed since the last check are not valid")
 
 
 # --------------------------------------------------------------------------- attention
@@ -413,12 +441,9 @@ def attention_prefill_tc(q, out, nh, kcache, vcache, page_table, page_size, cu_s
            "attention_prefill_tc")
 
 
-def attention_prefill_tc_status(head_dim: int, reset: bool = True) -> int:
+def attention_prefill_tc_status(head_dim: int = 0, reset: bool = True) -> int:
     """0, or the code of the first bounded wait that ran out in attention_prefill_tc (synchronizes)."""
-    lib = build.load("attention_prefill_tc", (("GB_HEAD_DIM", head_dim),))
-    lib.gb_attention_prefill_tc_status.argtypes = [c_int]
-    lib.gb_attention_prefill_tc_status.restype = c_int
-    return lib.gb_attention_prefill_tc_status(1 if reset else 0)
+    return _status("gb_attention_prefill_tc_status", reset)
 
 
 # --------------------------------------------------------------------------- sampling

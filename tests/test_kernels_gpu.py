@@ -337,3 +337,40 @@ def test_gemm_tc_persistent(k, m, n, kk, mode):
     k.gemm_tc_persistent(x, wg, out, swiglu=True, ctas=5)
     assert (out.float() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item() + 1e-6
     assert k.gemm_tc_status() == 0
+
+
+def test_dependent_launch_chain(k):
+    """The builds with programmatic dependent launch, which let a kernel start under the one before
+    it: a chain in which every kernel reads what the kernel before wrote (norm -> product ->
+    accumulating product -> norm), repeated on the same buffers, against the same chain computed
+    in float32.  A kernel that read or overwrote too early would show as a difference."""
+    from gemmars_b200.csrc import build
+    torch.manual_seed(5)
+    t, h, inter = 333, 512, 768
+    x0 = (torch.randn(t, h, device="cuda") * 0.5)
+    w_norm = (torch.rand(h, device="cuda") + 0.5).bfloat16().float()
+    w1 = (torch.randn(2 * inter, h, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(h, inter, device="cuda") * 0.05).bfloat16()
+
+    def plain(x):
+        for _ in range(3):
+            n = (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * w_norm).bfloat16().float()
+            g, u = n @ w1[:inter].float().T, n @ w1[inter:].float().T
+            a = (g / (1 + torch.exp(-g)) * u).bfloat16().float()
+            x = x + a @ w2.float().T
+        return x
+
+    want = plain(x0.clone())
+    build.set_pdl(True)
+    try:
+        x = x0.clone()
+        n = torch.empty(t, h, device="cuda", dtype=torch.bfloat16)
+        a = torch.empty(t, inter, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            k.rmsnorm(x, w_norm, n, 1e-6)
+            k.gemm_swiglu(n, w1, a)
+            k.gemm(a, w2, x, accumulate=True)
+    finally:
+        build.set_pdl(False)
+    assert (x - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    assert k.gemm_tc_status() == 0
