@@ -97,11 +97,11 @@ static inline int gb_launch_status() { return (int)cudaGetLastError(); }
 // what does not depend on that kernel (set-up, prefetch of weights) and calls pdl_wait_prior()
 // before it touches anything the earlier kernel wrote, or writes anything the earlier kernel may
 // still read.  pdl_release_next() lets the kernel after this one start in the same way.
-// Measured on the Qwen3-8B shape: a 2,048-token prompt, launched kernel by kernel, gets 5 %
+// Measured on the Qwen3-8B shape: a 2,048-token prompt, launched kernel by kernel, gets 2 %
 // shorter (the gaps between the large kernels close); the decode step replayed from a graph gains
-// nothing or loses (batch 64: -2 %), and the two instructions cost ~0.8 us a kernel even when a
-// launch carries no attribute.  So each unit exists in two builds and the engine calls the
-// GB_PDL=1 build for prompt steps and the plain build (no attribute, no instructions) for decoding.
+// 4 % at batch 1 and loses at batch 8 and 64, where the early kernel competes with the running
+// attention.  So each unit exists in two builds and the engine calls the GB_PDL=1 build for
+// prompt steps and the plain build (no attribute, no instructions) for decoding.
 #ifndef GB_PDL
 #define GB_PDL 0
 #endif
