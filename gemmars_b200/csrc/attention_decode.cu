@@ -16,6 +16,9 @@
 //
 // Each CTA leaves (m, l, o) per head in scratch; a second kernel merges the shares in order.
 // With one share the first kernel writes the result itself.
+// These kernels never start under the kernel before them: measured, the step got slower when the
+// attention CTAs, one to an SM, moved in early (batch 8: -6 %, batch 64: -14 %).
+#define GB_PDL_EARLY_START 0
 #include "mma.cuh"
 
 #ifndef GB_HEAD_DIM
@@ -43,7 +46,6 @@ attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
                         const int* __restrict__ seq_slot, int nh, int window, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int rows_per_chunk) {
   extern __shared__ float smem[];
-  pdl_release_next();
   pdl_wait_prior();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -165,6 +167,7 @@ attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __
   l0 = quad_sum(l0);
   l1 = quad_sum(l1);
 
+  pdl_release_next();   // this warp's keys are done: the next kernel may move in while the CTAs merge
   // ---- merge the warps of the CTA in warp order (shared memory: [WARPS][rows_per_chunk][HD + 2])
   const int R = rows_per_chunk, W = HD + 2;
   float* mine = smem + (size_t)warp * R * W;

@@ -101,7 +101,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint32_t* tmem_slot = (uint32_t*)(bars + 11);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
 
-  pdl_release_next();
   pdl_wait_prior();
   // ---- which sequence and which 128-token tile of it
   int b = 0, tile = blockIdx.x;
@@ -168,6 +167,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tma_load_2d(v_smem + s * V_BYTES, &map_v, 0, row * HD, &kv_full[s]);
       }
     }
+    if (lane == 0) pdl_release_next();   // the last page is on its way: the next kernel may move in
     __syncwarp();
   } else if (warp == 5) {
     // ---------------- MMA issue: S one page ahead of the softmax, then O += P V

@@ -80,7 +80,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb_begin = (int)((long long)kb_total * split / nsplit), kb_end = (int)((long long)kb_total * (split + 1) / nsplit);
   const int kb_count = kb_end - kb_begin;
 
-  pdl_release_next();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -127,6 +126,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (DUAL) tma_load_2d(a + W_BYTES, &map_w, (kb_begin + i) * BK, N + n0, &full_bar[s]);   // the up rows
         tma_load_2d(a + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
       }
+      // the last load is on its way: the next kernel may move in and ask for its first weights
+      // while this one finishes (earlier, its CTAs would only take room from this kernel's)
+      pdl_release_next();
     }
     __syncwarp();
   } else if (warp == 5) {
@@ -290,7 +292,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   const int tiles_m = (M + BN - 1) / BN, tiles_n = (N + BM - 1) / BM, tiles = tiles_m * tiles_n;
   const int kb_total = (K + BK - 1) / BK;
 
-  pdl_release_next();
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -335,6 +336,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           tma_load_2d(a + A_BYTES, &map_x, kb * BK, m0, &full_bar[s]);
         }
       }
+      pdl_release_next();   // all loads issued: the next kernel may move in
     }
     __syncwarp();
   } else if (warp == 5) {

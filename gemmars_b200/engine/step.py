@@ -202,14 +202,14 @@ class Runner:
             tok_pos=d_pos, tok_seq=d_seq, seq_slot=d_slot, seq_start=d_start, seq_len=d_len, cu_seqlens=d_cu,
             is_decode=bool((lens == 1).all()), max_new=int(lens.max()), max_total=max_total, cache=cache,
             page_size=cache.page_size)
-        # prompts run kernel by kernel: let each start under the one before (closes the launch gaps)
-        build.set_pdl(t > b)
+        # the builds whose kernels start under the tail of the kernel before them
+        build.set_pdl(True)
         try:
             x = self.model.forward(ctx, d_tokens)
+            logits = self.model.logits(ctx, x, d_rows) if rows else None
         finally:
             build.set_pdl(False)
         if rows:
-            logits = self.model.logits(ctx, x, d_rows)
             if contiguous:
                 out[dest[0]:dest[0] + len(dest)].copy_(logits)
             else:
@@ -276,16 +276,19 @@ class _DecodeGraph:
             tok_pos=self.d_pos, tok_seq=self.d_seq, seq_slot=self.d_slot, seq_start=self.d_start, seq_len=self.d_len,
             cu_seqlens=self.d_cu, is_decode=True, max_new=1, max_total=len_bucket, cache=runner.cache,
             page_size=runner.cache.page_size)
-        # once eagerly (loads the kernels, warms the allocator), then captured; plain launches
-        build.set_pdl(False)
-        torch.cuda.synchronize(dev)
-        self._forward()
-        torch.cuda.synchronize(dev)
-        before = kernels.launch_count()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, pool=runner._graph_pool()):
-            self.logits = self._forward()
-        self.launches = kernels.launch_count() - before
+        # once eagerly (loads the kernels, warms the allocator), then captured
+        build.set_pdl(True)
+        try:
+            torch.cuda.synchronize(dev)
+            self._forward()
+            torch.cuda.synchronize(dev)
+            before = kernels.launch_count()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph, pool=runner._graph_pool()):
+                self.logits = self._forward()
+            self.launches = kernels.launch_count() - before
+        finally:
+            build.set_pdl(False)
 
     def _forward(self):
         model = self.runner.model
