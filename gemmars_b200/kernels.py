@@ -312,7 +312,7 @@ def gemm_swiglu(x, w_gate_up, out):
     silu_mul(gu, out)
 
 
-_STATUS_ENTRIES = ("gb_gemm_tc_status", "gb_attention_prefill_tc_status")
+_STATUS_ENTRIES = ("gb_gemm_tc_status", "gb_attention_prefill_tc_status", "gb_attention_decode_stream_status")
 
 
 def _status(entry: str, reset: bool) -> int:
@@ -397,6 +397,54 @@ def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos,
              seq_slot.data_ptr(), ntok, nh, window or 0, shares, _ptr(scratch), _stream()), "attention_decode")
     if shares > 1:
         count_launches(1)   # the merge kernel
+
+
+STREAM_DECODE_HEAD_DIMS = (64, 128)
+STREAM_DECODE_MAX_TOKENS = 4096
+_decode_stream_scratch = {}
+
+
+def attention_decode_stream_usable(ntok: int, nh: int, nkv: int, hd: int, page_size: int) -> bool:
+    return (hd in STREAM_DECODE_HEAD_DIMS and page_size == 64 and nh % nkv == 0 and nh // nkv <= 16
+            and ntok <= STREAM_DECODE_MAX_TOKENS)
+
+
+def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot,
+                            window=None, ctas=None):
+    """bfloat16 attention of single positions with the cache streamed through shared memory by
+    TMA: the pages that the step reads are dealt evenly to the CTAs as one flat list, whatever the
+    lengths of the sequences; parts of a (token, kv head) that fall to different CTAs are added
+    in key order by a second kernel."""
+    _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot)
+    nkv, hd = kcache.shape[1], kcache.shape[3]
+    ntok = q.shape[0]
+    assert q.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and kcache.dtype == torch.bfloat16
+    assert q.stride(-1) == 1 and out.stride(-1) == 1 and vcache.shape[2:] == (hd, page_size)
+    assert kcache.is_contiguous() and vcache.is_contiguous()
+    if not attention_decode_stream_usable(ntok, nh, nkv, hd, page_size):
+        raise KernelError(f"attention_decode_stream: head size {hd} (64 or 128), page size {page_size} (64), "
+                          f"{nh // max(nkv, 1)} query heads per kv head (at most 16) or {ntok} tokens "
+                          f"(at most {STREAM_DECODE_MAX_TOKENS}) not supported")
+    defines = (("GB_HEAD_DIM", hd),)
+    sig = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int,
+           c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    f = _fn("attention_decode_stream", "gb_attention_decode_stream", sig, defines=defines)
+    if ctas is None:
+        ctas = _SM_COUNT   # measured at 8,192 keys, batch 1 / 8 / 64: 17 / 54 / 323 us; two per SM: 24 / 58 / 329
+    need = ctas * 2 * (nh // nkv) * (hd + 2) + ntok + 1
+    scratch = _decode_stream_scratch.get(q.device.index)
+    if scratch is None or scratch.numel() < need:
+        scratch = _decode_stream_scratch[q.device.index] = torch.empty(max(need, 1 << 20), dtype=torch.float32,
+                                                                       device=q.device)
+    _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
+             kcache.shape[0], page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(),
+             tok_seq.data_ptr(), seq_slot.data_ptr(), ntok, nh, window or 0, ctas, scratch.data_ptr(), _stream()),
+           "attention_decode_stream")
+    count_launches(1)   # the merge kernel
+
+
+def attention_decode_stream_status(reset: bool = True) -> int:
+    return _status("gb_attention_decode_stream_status", reset)
 
 
 def attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, cu_seqlens, seq_start, seq_slot, window=None):
@@ -491,7 +539,10 @@ def attention_units(compute: str, head_dim: int):
         return [("attention_ref", ())]
     hd = (("GB_HEAD_DIM", head_dim),)
     prefill = "attention_prefill_tc" if head_dim in (64, 128) else "attention_prefill"
-    return [("attention_ref", ()), ("attention_decode", hd), (prefill, hd)]
+    units = [("attention_ref", ()), ("attention_decode", hd), (prefill, hd)]
+    if head_dim in STREAM_DECODE_HEAD_DIMS:
+        units.append(("attention_decode_stream", hd))
+    return units
 
 
 def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=None):
@@ -500,6 +551,10 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
     position does not depend on the batch."""
     if q.dtype == torch.bfloat16 and ctx.max_new <= DECODE_KERNEL_MAX_NEW:
         nkv = kcache.shape[1]
+        if attention_decode_stream_usable(ctx.n_tokens, nh, nkv, kcache.shape[3], page_size):
+            attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq,
+                                    ctx.seq_slot, window)
+            return
         shares = decode_shares(ctx.n_tokens, nh, nkv, ctx.max_total if window is None else min(ctx.max_total, window))
         attention_decode(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
                          window, shares)

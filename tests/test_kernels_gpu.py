@@ -223,6 +223,37 @@ def test_attention_kernels_against_plain(k, hd, nh, nkv, window):
                 assert err <= tol * max(1.0, ref.abs().max().item()), f"shares={shares}: {err}"
 
 
+@pytest.mark.parametrize("hd,nh,nkv,window,ring", [(64, 4, 2, None, None), (128, 8, 2, 100, None), (64, 12, 1, None, None),
+                                                    (128, 32, 8, None, None), (128, 6, 3, 128, 3), (64, 16, 1, 70, None)])
+def test_attention_decode_stream_against_plain(k, hd, nh, nkv, window, ring):
+    """The decode kernel that streams pages through shared memory, with sequences of very unequal
+    lengths (so that CTAs' ranges cut some (token, kv head) pairs into parts and hold others
+    whole), with few and many CTAs (more CTAs than pages: some get none), a window's edge, a ring
+    of pages, a planted far key, and scratch memory that starts out as NaN."""
+    torch.manual_seed(hd + nh)
+    lengths = [700, 64, 1, 131, 65, 2, 300]
+    n = len(lengths)
+    kc, vc, table, dense = _paged(n, lengths, nkv, hd, torch.bfloat16, seed=hd + 1, ring=ring)
+    tok_seq = torch.arange(n, dtype=torch.int32, device="cuda")
+    tok_pos = torch.tensor([x - 1 for x in lengths], dtype=torch.int32, device="cuda")
+    seq_slot = torch.arange(n, dtype=torch.int32, device="cuda")
+    q = (torch.randn(n, nh * hd, device="cuda") * hd ** -0.5).bfloat16()
+    far = 3 if window is None else max(0, lengths[0] - window)
+    q[0, :hd] = (dense[0][0][far, 0] * (6.0 / hd ** 0.5)).bfloat16()
+    ref = torch.stack([_attn_ref(q[i].float().view(nh, hd), *dense[i], lengths[i] - 1, nh, window).view(-1)
+                       for i in range(n)])
+    k.attention_decode_stream(q, torch.zeros_like(q), nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window)
+    for ctas in (None, 1, 2, 7, 500):
+        k._decode_stream_scratch[q.device.index].fill_(float("nan"))
+        out = torch.zeros_like(q)
+        k.attention_decode_stream(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, ctas=ctas)
+        err = (out.float() - ref).abs().max().item()
+        assert err <= 2 ** -7 * max(1.0, ref.abs().max().item()), f"ctas={ctas}: {err}"
+    assert k.attention_decode_stream_status() == 0
+    with pytest.raises(k.KernelError):
+        k.attention_decode_stream(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, ctas=5000)
+
+
 @pytest.mark.parametrize("hd,nh,nkv,window", [(16, 4, 2, None), (32, 6, 3, 40), (48, 5, 1, None), (128, 8, 2, 100),
                                                (64, 12, 12, None)])
 def test_attention_prefill_against_plain(k, hd, nh, nkv, window):
