@@ -43,17 +43,26 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ rows_index, int n, float eps) {
   __shared__ float scratch[33];
   pdl_release_next();
+  constexpr int KEEP = 4;            // float4s a thread keeps in registers between the two passes
+  const bool vec = (n & 3) == 0, keep = vec && n / 4 <= KEEP * (int)blockDim.x;
+  float4 gain[KEEP];
+  if (keep) {
+    // the weights do not depend on the kernel before this one: asked for before waiting for it
+#pragma unroll
+    for (int u = 0; u < KEEP; ++u) {
+      const int i = threadIdx.x + u * blockDim.x;
+      gain[u] = i < n / 4 ? ((const float4*)w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
   pdl_wait_prior();
   const int r = blockIdx.x;
   const float* row = x + (size_t)(rows_index ? rows_index[r] : r) * n;
   T* o = out + (size_t)r * n;
   // four elements at a time when the row allows it (rows of x and out are then 16-byte aligned);
   // the order of the additions depends on n and the block size alone
-  if ((n & 3) == 0) {
+  if (vec) {
     const float4* row4 = (const float4*)row;
     const float4* w4 = (const float4*)w;
-    constexpr int KEEP = 4;            // float4s a thread keeps in registers between the two passes
-    const bool keep = n / 4 <= KEEP * (int)blockDim.x;
     float4 held[KEEP];
     float ss = 0.f;
     if (keep) {
@@ -73,7 +82,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)n + eps);
     for (int u = 0, i = threadIdx.x; i < n / 4; i += blockDim.x, ++u) {
-      const float4 v = keep ? held[u < KEEP ? u : 0] : row4[i], g = w4[i];
+      const float4 v = keep ? held[u < KEEP ? u : 0] : row4[i], g = keep ? gain[u < KEEP ? u : 0] : w4[i];
       const float a = v.x * inv * g.x, b = v.y * inv * g.y, c = v.z * inv * g.z, d = v.w * inv * g.w;
       if (sizeof(T) == 4) {
         ((float4*)o)[i] = make_float4(a, b, c, d);
@@ -119,8 +128,7 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
                                                          int rot, const float* __restrict__ qw,
                                                          const float* __restrict__ kw, float eps,
                                                          const float* __restrict__ cs, const float* __restrict__ sn,
-                                                         float q_scale, const int* __restrict__ tok_seq,
-                                                         const int* __restrict__ seq_slot, const PagedKV& kv,
+                                                         float q_scale, int page, const PagedKV& kv,
                                                          T* __restrict__ kcache, T* __restrict__ vcache, int flags) {
   const int lane = threadIdx.x & 31;
   const int heads = nh + 2 * nkv;
@@ -128,7 +136,7 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
   const bool cache = flags & FLAG_CACHE;
   if (h >= nh + nkv) {  // value head
     if (!cache || (flags & FLAG_V_TILED)) return;   // tiled: value_cache_tile_kernel writes the values
-    T* dst = vcache + kv.vcol(seq_slot[tok_seq[t]], pos, h - nh - nkv);
+    T* dst = vcache + ((size_t)page * nkv + (h - nh - nkv)) * kv.page_size * hd + pos % kv.page_size;
     for (int i = lane; i < hd; i += 32) dst[(size_t)i * kv.page_size] = src[i];
     return;
   }
@@ -140,7 +148,8 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
     // stores), so the head is read once for the norm and the rotation alike
     const int half = hd / 2;
     const float scale = is_q ? q_scale : 1.f;
-    bf16* cdst = (!is_q && cache) ? (bf16*)kcache + kv.row(seq_slot[tok_seq[t]], pos, h - nh) : nullptr;
+    bf16* cdst = (!is_q && cache) ? (bf16*)kcache + (((size_t)page * nkv + (h - nh)) * kv.page_size + pos % kv.page_size) * hd
+                                  : nullptr;
     const bf16* s16 = (const bf16*)src;
     float2 a[2], b[2];   // up to head size 256: two rounds of 64 dims per half
     float ss = 0.f;
@@ -153,6 +162,15 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
         ss += a[r].x * a[r].x + a[r].y * a[r].y + b[r].x * b[r].x + b[r].y * b[r].y;
       }
     }
+    float2 wa[2], wb[2];   // the norm's weights for the same dims, asked for before the sum is known
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int i = 2 * lane + 64 * r;
+      if ((flags & FLAG_NORM) && i < half) {
+        wa[r] = *(const float2*)(w + i);
+        wb[r] = *(const float2*)(w + i + half);
+      }
+    }
     float inv = 1.f;
     if (flags & FLAG_NORM) inv = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
 #pragma unroll
@@ -161,7 +179,7 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
       if (i < half) {
         float ax = a[r].x * inv, ay = a[r].y * inv, bx = b[r].x * inv, by = b[r].y * inv;
         if (flags & FLAG_NORM) {
-          ax *= w[i]; ay *= w[i + 1]; bx *= w[i + half]; by *= w[i + half + 1];
+          ax *= wa[r].x; ay *= wa[r].y; bx *= wb[r].x; by *= wb[r].y;
         }
         const float s0 = sn[i], c0 = cs[i], s1 = sn[i + 1], c1 = cs[i + 1];
         const __nv_bfloat162 ra = __floats2bfloat162_rn((ax * c0 - bx * s0) * scale, (ay * c1 - by * s1) * scale);
@@ -189,7 +207,7 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
     inv = 1.0f / sqrtf(ss / (float)hd + eps);
   }
   const float scale = is_q ? q_scale : 1.f;
-  T* cdst = (!is_q && cache) ? kcache + kv.row(seq_slot[tok_seq[t]], pos, h - nh) : nullptr;
+  T* cdst = (!is_q && cache) ? kcache + (((size_t)page * nkv + (h - nh)) * kv.page_size + pos % kv.page_size) * hd : nullptr;
   const bool inplace = flags & FLAG_INPLACE;
   const bool rope = flags & FLAG_ROPE;
   const int half = rope ? rot / 2 : 0;
@@ -219,15 +237,19 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
   }
 }
 
-// One CTA per token: the token's rot / 2 angles (float32(position) * inv_freq, as the reference)
-// and their cos and sin are computed once into shared memory, then the warps take the heads in turn.
+// A CTA takes `heads_per_cta` heads of one token (grid: tokens x groups of heads): the token's
+// rot / 2 angles (float32(position) * inv_freq, as the reference) and their cos and sin are computed
+// once into shared memory and the token's page is looked up once, while the heads' loads are already
+// on their way; then the warps take the heads in turn.  Prompts give a CTA all heads of a token (the
+// angles are computed once per token); decoding gives every warp one head, since there the kernel
+// is a chain of latencies and not work.
 template <typename T>
 __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int nh, int nkv, int hd, int rot,
                                             const float* __restrict__ qw, const float* __restrict__ kw, float eps,
                                             const float* __restrict__ inv_freq, float q_scale,
                                             const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                             const int* __restrict__ seq_slot, PagedKV kv, T* __restrict__ kcache,
-                                            T* __restrict__ vcache, int flags) {
+                                            T* __restrict__ vcache, int flags, int heads_per_cta) {
   extern __shared__ float trig[];   // cos [rot / 2], sin [rot / 2]
   pdl_release_next();
   pdl_wait_prior();
@@ -236,12 +258,16 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
   const int half = (flags & FLAG_ROPE) ? rot / 2 : 0;
   float* cs = trig;
   float* sn = trig + half;
+  int page = 0;
+  if (flags & FLAG_CACHE)
+    page = kv.page_table[(size_t)seq_slot[tok_seq[t]] * kv.table_width + (pos / kv.page_size) % kv.table_width];
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
   __syncthreads();
-  const int heads = nh + 2 * nkv;
-  for (int h = threadIdx.x >> 5; h < heads; h += blockDim.x >> 5)
-    head_norm_rope_cache_one<T>(qkv, t, h, pos, nh, nkv, hd, rot, qw, kw, eps, cs, sn, q_scale, tok_seq, seq_slot, kv, kcache,
-                                vcache, flags);
+  const int heads = nh + 2 * nkv, h0 = blockIdx.y * heads_per_cta;
+  const int h1 = min(heads, h0 + heads_per_cta);
+  for (int h = h0 + (threadIdx.x >> 5); h < h1; h += blockDim.x >> 5)
+    head_norm_rope_cache_one<T>(qkv, t, h, pos, nh, nkv, hd, rot, qw, kw, eps, cs, sn, q_scale, page, kv, kcache, vcache,
+                                flags);
 }
 
 // The values of 32 consecutive packed tokens for one kv head, written into the cache through a
@@ -287,16 +313,19 @@ GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, in
   PagedKV kv{page_table, table_width, page_size, nkv, hd};
   const bool v_tiled = (flags & FLAG_CACHE) && nkv > 0 && ntok >= 64;   // prompts: values through the transposing kernel
   if (v_tiled) flags |= FLAG_V_TILED;
-  const int threads = (nh + 2 * nkv) >= 8 ? 256 : 32 * (nh + 2 * nkv);
+  const int heads = nh + 2 * nkv;
+  const int threads = heads >= 8 ? 256 : 32 * heads;
+  const int heads_per_cta = ntok >= 64 ? heads : threads / 32;
+  const dim3 grid(ntok, (heads + heads_per_cta - 1) / heads_per_cta);
   const size_t trig_bytes = (size_t)rot * sizeof(float);
   if (dtype == GB_F32)
-    gb_launch(head_norm_rope_cache_kernel<float>, ntok, threads, trig_bytes, stream,
+    gb_launch(head_norm_rope_cache_kernel<float>, grid, threads, trig_bytes, stream,
         (float*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
-        (float*)kcache, (float*)vcache, flags);
+        (float*)kcache, (float*)vcache, flags, heads_per_cta);
   else if (dtype == GB_BF16)
-    gb_launch(head_norm_rope_cache_kernel<bf16>, ntok, threads, trig_bytes, stream,
+    gb_launch(head_norm_rope_cache_kernel<bf16>, grid, threads, trig_bytes, stream,
         (bf16*)qkv, ntok, nh, nkv, hd, rot, qw, kw, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv,
-        (bf16*)kcache, (bf16*)vcache, flags);
+        (bf16*)kcache, (bf16*)vcache, flags, heads_per_cta);
   else
     return GB_ERR_DTYPE;
   int rc = gb_launch_status();

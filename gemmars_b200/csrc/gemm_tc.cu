@@ -40,6 +40,22 @@ enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3
 
 __device__ int g_status;   // first failure of any launch; 0 when all waits completed
 
+// -DGB_TRACE: thread 0 of every CTA of gemm_tc_kernel stamps the global timer at eight points
+// (entry, set-up done, first and last operands, accumulator done, cluster barrier, stored, exit);
+// gb_gemm_tc_trace copies the stamps of the last launch out.  For finding where a launch's time goes.
+#ifdef GB_TRACE
+__device__ unsigned long long g_trace[4096 * 8];
+__device__ __forceinline__ void trace(int slot) {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+  if (cta < 4096) g_trace[cta * 8 + slot] = t;
+}
+#define TRACE(slot) trace(slot)
+#else
+#define TRACE(slot)
+#endif
+
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
 
@@ -81,6 +97,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb_count = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
+    TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -96,6 +113,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  if (threadIdx.x == 0) TRACE(1);
 
   if (warp == 4) {
     // ---------------- TMA producer
@@ -143,6 +161,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           break;
         }
         tc_fence_after();
+        if (i == 0) TRACE(2);
+        if (i == kb_count - 1) TRACE(3);
         const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES), udesc = smem_desc(a + W_BYTES);
 #pragma unroll
@@ -160,20 +180,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   // ---------------- epilogue (warps 0-3); the other warps wait at the barriers below
   float* partial = (float*)smem;   // [ACC_COLS][BM] float32, over the pipeline stages (idle by then)
   bool have_acc = false;
+  // with the inner dimension split, every rank adds a share of the tile's real tokens over all ranks
+  const int real = min(M - m0, BN), share = (real + (int)nsplit - 1) / (int)nsplit;
+  const int c0 = min(real, (int)split * share), c1 = min(real, c0 + share);
+  float bias_v = 0.f, old[8];
   if (warp < 4) {
+    pdl_wait_prior();   // y may be read (accumulate) and is written: not before the kernel before is done
+    const int n = n0 + warp * 32 + lane;
+    bias_v = (bias && n < N) ? bias[n] : 0.f;
+    if (MODE == EPI_ACCUMULATE_F32 && nsplit > 1) {
+      // what this thread will add to: asked for now, so that the answer is there after the products
+#pragma unroll
+      for (int i = 0; i < 8; ++i) old[i] = (c0 + i < c1 && n < N) ? ((const float*)y)[(size_t)(m0 + c0 + i) * ldy + n] : 0.f;
+    }
     if (kb_count > 0) {
       have_acc = __all_sync(0xffffffffu, mbar_wait(tmem_bar, 0));   // the same answer in every lane
       if (!have_acc && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
     }
     tc_fence_after();
-    pdl_wait_prior();   // y may be read (accumulate) and is written: not before the kernel before is done
+    if (threadIdx.x == 0) TRACE(4);
   }
   if (nsplit > 1) {
-    // every rank publishes its partial sums, then adds a share of the tokens over all ranks
+    // every rank publishes its partial sums, then adds its share of the tokens in rank order
     if (warp < 4) {
       const int f = warp * 32 + lane;
 #pragma unroll 1
       for (int c = 0; c < (int)ACC_COLS; c += 16) {
+        if ((c % BN) >= real) continue;
         uint32_t v[16];
         if (have_acc) {
           tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
@@ -187,38 +220,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     cluster_sync();
+    if (threadIdx.x == 0) TRACE(5);
     if (warp < 4) {
-      // every rank adds its own share of the tile's tokens over all ranks, in rank order; the
-      // loads of one token are all in flight together
       const int f = warp * 32 + lane, n = n0 + f;
-      const float b = (bias && n < N) ? bias[n] : 0.f;
-      const int cols = BN / (int)nsplit, c0 = (int)split * cols;
-#pragma unroll 2
-      for (int c = c0; c < c0 + cols; ++c) {
-        const int m = m0 + c;
-        if (m >= M) break;
-        float v[8], u[8];
+      constexpr int CH = DUAL ? 2 : 4;   // tokens whose loads are in flight together (8 ranks each)
+#pragma unroll 1
+      for (int base = c0; base < c1; base += CH) {
+        float v[CH][8], u[CH][8];
 #pragma unroll
-        for (uint32_t r = 0; r < 8; ++r) {
-          v[r] = r < nsplit ? ld_peer_f32(&partial[c * BM + f], r) : 0.f;
-          if (DUAL) u[r] = r < nsplit ? ld_peer_f32(&partial[(BN + c) * BM + f], r) : 0.f;
+        for (int i = 0; i < CH; ++i) {
+          const int c = min(base + i, c1 - 1);
+#pragma unroll
+          for (uint32_t r = 0; r < 8; ++r) {
+            v[i][r] = r < nsplit ? ld_peer_f32(&partial[c * BM + f], r) : 0.f;
+            if (DUAL) u[i][r] = r < nsplit ? ld_peer_f32(&partial[(BN + c) * BM + f], r) : 0.f;
+          }
         }
-        float acc = v[0];
 #pragma unroll
-        for (int r = 1; r < 8; ++r) acc += v[r];
-        if (DUAL) {
-          float up = u[0];
+        for (int i = 0; i < CH; ++i) {
+          const int c = base + i;
+          if (c >= c1 || n >= N) continue;
+          float acc = v[i][0];
 #pragma unroll
-          for (int r = 1; r < 8; ++r) up += u[r];
-          acc = silu_mul(acc, up);
+          for (int r = 1; r < 8; ++r) acc += v[i][r];
+          if (DUAL) {
+            float up = u[i][0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) up += u[i][r];
+            acc = silu_mul(acc, up);
+          }
+          const size_t idx = (size_t)(m0 + c) * ldy + n;
+          if (MODE == EPI_ACCUMULATE_F32) {
+            float prev = 0.f;   // old[c - c0] without indexing registers by a variable
+#pragma unroll
+            for (int q = 0; q < 8; ++q) prev = (c - c0 == q) ? old[q] : prev;
+            ((float*)y)[idx] = prev + acc + bias_v;
+          } else {
+            emit<MODE>(y, idx, acc + bias_v);
+          }
         }
-        if (n < N) emit<MODE>(y, (size_t)m * ldy + n, acc + b);
       }
     }
     cluster_sync();  // every rank keeps its shared memory until the others have read it
   } else if (warp < 4 && have_acc) {
     const int f = warp * 32 + lane, n = n0 + f;
-    const float b = (bias && n < N) ? bias[n] : 0.f;
+    const float b = bias_v;
 #pragma unroll 1
     for (int c = 0; c < BN; c += 16) {
       if (m0 + c >= M) break;
@@ -258,10 +304,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
   }
+  if (threadIdx.x == 0) TRACE(6);
   tc_fence_before();
   __syncthreads();
   __syncwarp();
   if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+  if (threadIdx.x == 0) TRACE(7);
 }
 
 // ------------------------------------------------------------------ the persistent kernel for prompts
@@ -579,6 +627,12 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
   }
   return GB_ERR_ARG;
 }
+
+#ifdef GB_TRACE
+GB_EXPORT int gb_gemm_tc_trace(unsigned long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
+}
+#endif
 
 // The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator).
 // Synchronizes the device; for tests and health checks, not for the step.
