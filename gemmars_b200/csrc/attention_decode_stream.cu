@@ -117,7 +117,8 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     *abort = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  pdl_wait_prior();
+  // Positions, slots and the page table are the step's inputs, not the work of the kernel before
+  // this one: the lists of pages are made before waiting for it; q and the cache are read after.
   // ---- pages per token, then their running sum (warp 0, 32 tokens a round)
   for (int t = threadIdx.x; t < ntok; t += THREADS) prefix[t + 1] = token_span(t, tok_pos, tok_seq, seq_slot, window).pages;
   __syncthreads();
@@ -137,8 +138,6 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     if (lane == 0) prefix[0] = 0;
   }
   __syncthreads();
-  if (blockIdx.x == 0)
-    for (int t = threadIdx.x; t <= ntok; t += THREADS) prefix_out[t] = prefix[t];
   const long long P = (long long)prefix[ntok] * nkv, G = gridDim.x;
   const long long p0 = (long long)blockIdx.x * P / G, p1 = ((long long)blockIdx.x + 1) * P / G;
 
@@ -159,6 +158,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
       return page_table[(size_t)sp.slot * table_width + (sp.first_page + page) % table_width] * nkv + kvh;
     };
     int next_row = lookup(p0 + lane);
+    pdl_wait_prior();
     uint32_t it = 0;
     bool ok = true;
     for (long long base = p0; base < p1; base += 32) {
@@ -198,6 +198,9 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
   uint32_t it = 0, seg = 0;
   long long p = p0;
   int t = p0 < p1 ? token_of(prefix, ntok, nkv, p0) : 0;
+  pdl_wait_prior();
+  if (blockIdx.x == 0)
+    for (int i = threadIdx.x; i <= ntok; i += CW * 32) prefix_out[i] = prefix[i];
   while (p < p1) {
     // ---- the segment: (token t, kv head kvh), pages [a, b) of the token's span
     const TokenSpan sp = token_span(t, tok_pos, tok_seq, seq_slot, window);
@@ -352,20 +355,59 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
 // MERGE_EPT when there are more than 1,024); the parts' maxima and sums are fetched by all
 // threads at once and turned into one factor per part and head, so that the thread's own loads
 // of o depend on nothing and go out together.  More than MERGE_ROUND parts take several rounds.
-constexpr int MAX_CTAS = 1024, MERGE_ROUND = 64, MERGE_EPT = 4, MAX_REP = 16;
+constexpr int MAX_CTAS = 1024, MERGE_ROUND = 64, MERGE_EPT = 4, MAX_REP = 16, MERGE_COUNT_ITSELF = 256;
 __global__ void __launch_bounds__(1024)
 attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_stride, const float* __restrict__ part,
-                                     const int* __restrict__ prefix, int ntok, int nkv, int nh, int G) {
+                                     const int* __restrict__ prefix, const int* __restrict__ tok_pos, int window,
+                                     int ntok, int nkv, int nh, int G) {
   __shared__ int slot_of[MERGE_ROUND];   // scratch slot of a part; -1: that CTA had no pages at all
   __shared__ float fac[MERGE_ROUND][MAX_REP], sum[MERGE_ROUND][MAX_REP];
   __shared__ float run_m[MAX_REP], run_l[MAX_REP], scale[MAX_REP];
+  __shared__ int span[3];                // pages before token t, through token t, of all tokens
   pdl_release_next();
-  pdl_wait_prior();
   const int t = blockIdx.x / nkv, kvh = blockIdx.x % nkv;
+  if (ntok <= MERGE_COUNT_ITSELF) {
+    // with few tokens the CTA counts the pages itself, from the step's inputs, while the stream
+    // kernel is still running; else it reads the stream kernel's list once that is done
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      int carry = 0;
+      for (int base = 0; base < ntok; base += 32) {
+        const int i = base + lane;
+        int v = 0;
+        if (i < ntok) {
+          const int hi = tok_pos[i] + 1, lo = window > 0 ? max(0, hi - window) : 0;
+          v = (hi - 1) / KEYS - lo / KEYS + 1;
+        }
+        int incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int up = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += up;
+        }
+        if (i == t) {
+          span[0] = carry + incl - v;
+          span[1] = carry + incl;
+        }
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) span[2] = carry;
+    }
+    __syncthreads();
+    pdl_wait_prior();
+  } else {
+    pdl_wait_prior();
+    if (threadIdx.x == 0) {
+      span[0] = prefix[t];
+      span[1] = prefix[t + 1];
+      span[2] = prefix[ntok];
+    }
+    __syncthreads();
+  }
   const int rep = nh / nkv, W = HD + 2;
-  const long long P = (long long)prefix[ntok] * nkv;
-  const int pages = prefix[t + 1] - prefix[t];
-  const long long u0 = (long long)prefix[t] * nkv + (long long)kvh * pages, u1 = u0 + pages;
+  const long long P = (long long)span[2] * nkv;
+  const int pages = span[1] - span[0];
+  const long long u0 = (long long)span[0] * nkv + (long long)kvh * pages, u1 = u0 + pages;
   const int first = (int)(((u0 + 1) * G - 1) / P), last = (int)((u1 * G - 1) / P);
   if (first == last) return;
   const int n = last - first + 1, tid = threadIdx.x, nthr = blockDim.x;
@@ -475,15 +517,18 @@ GB_EXPORT int gb_attention_decode_stream(const void* q, long long q_stride, void
   }
   float* part = scratch;
   int* prefix = (int*)(scratch + (size_t)ctas * 2 * rep * (HD + 2));
-  {
-    // this kernel never starts under the kernel before it (see attention_decode.cu): plain launch
-    attention_decode_stream_kernel<<<ctas, THREADS, smem, stream>>>(
-        mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq,
-        seq_slot, ntok, nh, window, part, prefix);
-  }
+#ifdef GB_STREAM_PLAIN_LAUNCH
+  attention_decode_stream_kernel<<<ctas, THREADS, smem, stream>>>(
+      mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq,
+      seq_slot, ntok, nh, window, part, prefix);
+#else
+  gb_launch(attention_decode_stream_kernel, dim3(ctas), dim3(THREADS), smem, stream, mk, mv, (const bf16*)q, q_stride,
+            (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq, seq_slot, ntok, nh, window, part,
+            prefix);
+#endif
   const int merge_threads = rep * HD >= 1024 ? 1024 : (rep * HD + 31) / 32 * 32;
   gb_launch(attention_decode_stream_merge_kernel, dim3(ntok * nkv), dim3(merge_threads), 0, stream, (bf16*)out, out_stride,
-            (const float*)part, (const int*)prefix, ntok, nkv, nh, ctas);
+            (const float*)part, (const int*)prefix, tok_pos, window, ntok, nkv, nh, ctas);
   return gb_launch_status();
 }
 
