@@ -237,7 +237,7 @@ def main():
     # ---- prefill of 2,048 tokens
     toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
     pre_ms = []
-    for it in range(4):
+    for it in range(8):
         s = runner.open()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
