@@ -192,7 +192,7 @@ def test_head_norm_rope_cache(k, dtype, hd, rot, nh, nkv):
 
 
 @pytest.mark.parametrize("hd,nh,nkv,window", [(16, 4, 2, None), (32, 6, 3, 40), (48, 5, 1, None), (128, 8, 2, 100),
-                                               (64, 12, 1, None), (128, 32, 1, None)])
+                                               (64, 12, 1, None), (128, 32, 1, None), (96, 3, 1, 50), (256, 4, 2, None)])
 def test_attention_kernels_against_plain(k, hd, nh, nkv, window):
     """The plain kernel in both precisions and the decode kernel (1 and several shares), with a
     planted far key: one key far back gets a score that stands out, so a kernel that drops or
@@ -255,7 +255,7 @@ def test_attention_decode_stream_against_plain(k, hd, nh, nkv, window, ring):
 
 
 @pytest.mark.parametrize("hd,nh,nkv,window", [(16, 4, 2, None), (32, 6, 3, 40), (48, 5, 1, None), (128, 8, 2, 100),
-                                               (64, 12, 12, None)])
+                                               (64, 12, 12, None), (96, 3, 1, 50), (256, 4, 2, None)])
 def test_attention_prefill_against_plain(k, hd, nh, nkv, window):
     """Packed prompts of unequal lengths, some continuing a sequence that is already cached; every
     token against the plain statement.  Sequence 1's last query points at a far key."""
