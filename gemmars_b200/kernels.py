@@ -496,15 +496,28 @@ def attention_prefill_tc_status(head_dim: int = 0, reset: bool = True) -> int:
 
 # --------------------------------------------------------------------------- sampling
 
-def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None):
+_sample_scratch = {}
+
+
+def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None, wide=False):
     """out[r] = token drawn from logits[r] (float32 [rows, vocab]).  Rows whose temperature is
-    <= 0 (or all rows when ``temperature`` is None) take the first maximum."""
+    <= 0 (or all rows when ``temperature`` is None) take the first maximum.  Rows with top_k = 0
+    (all tokens) or more than MAX_TOP_K candidates need ``wide``: they are sorted in scratch memory
+    of 20 bytes per logit."""
     _cuda(logits, out, temperature, top_k, top_p, uniform)
     assert logits.dtype == torch.float32 and logits.stride(-1) == 1 and out.dtype == torch.int32
+    scratch = None
+    if wide and temperature is not None:
+        need = 5 * logits.shape[0] * logits.shape[1]
+        scratch = _sample_scratch.get(logits.device.index)
+        if scratch is None or scratch.numel() < need:
+            scratch = _sample_scratch[logits.device.index] = torch.empty(need, dtype=torch.float32, device=logits.device)
     f = _fn("sampling", "gb_sample",
-            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
-             _ptr(top_p), _ptr(uniform), out.data_ptr(), _stream()), "sample")
+             _ptr(top_p), _ptr(uniform), out.data_ptr(), _ptr(scratch), _stream()), "sample")
+    if scratch is not None:
+        count_launches(1)
 
 
 # --------------------------------------------------------------------------- choices by precision and shape

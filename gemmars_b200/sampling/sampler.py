@@ -47,12 +47,17 @@ class SamplingParams:
     def greedy(self) -> bool:
         return self.temperature <= 0.0
 
+    @property
+    def wide(self) -> bool:
+        """More candidates than the device sampler keeps in shared memory (top_k = 0: all tokens,
+        src/sampler.rs:43-47): such rows are sorted in global memory, which is slower."""
+        return not self.greedy and not 1 <= self.top_k <= kernels.MAX_TOP_K
+
     def check(self) -> None:
         if self.greedy:
             return
-        if not 1 <= self.top_k <= kernels.MAX_TOP_K:
-            raise ValueError(f"top_k must be between 1 and {kernels.MAX_TOP_K} when temperature > 0 "
-                             f"(got {self.top_k}); the device sampler keeps its candidates in shared memory")
+        if self.top_k < 0:
+            raise ValueError(f"top_k must be 0 (all tokens) or positive, got {self.top_k}")
         if not 0.0 < self.top_p:
             raise ValueError(f"top_p must be positive, got {self.top_p}")
 
@@ -67,6 +72,7 @@ class BatchSampler:
         self.rngs = [Xorshift64Star(p.seed) for p in params]
         self.device = device
         self.all_greedy = all(p.greedy for p in params)
+        self.any_wide = any(p.wide for p in params)
 
     def sample(self, logits: torch.Tensor, seqs: Sequence[int]) -> List[int]:
         """``logits``: float32 [len(seqs), vocab] on the device; ``seqs``: which sequence each
@@ -85,5 +91,5 @@ class BatchSampler:
         us = [0.0 if self.params[s].greedy else self.rngs[s].next_f32() for s in seqs]
         f = torch.tensor([temps, ps, us], dtype=torch.float32).pin_memory().to(logits.device, non_blocking=True)
         k = torch.tensor(ks, dtype=torch.int32).pin_memory().to(logits.device, non_blocking=True)
-        kernels.sample(logits, out, f[0], k, f[1], f[2])
+        kernels.sample(logits, out, f[0], k, f[1], f[2], wide=self.any_wide)
         return out

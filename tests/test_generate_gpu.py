@@ -84,9 +84,12 @@ def test_device_sampler_matches_the_plain_sampler():
     logits = (rng.standard_normal((6, vocab)) * 3).astype(np.float32)
     logits[1, 100] = logits[1, 2000] = logits[1].max() + 1.0        # a tie at the top: lower id wins
     logits[4, :50] = 2.5                                               # many ties around the k-th place
-    params = [(0.0, 64, 0.95), (0.0, 64, 0.95), (0.7, 64, 0.95), (1.3, 1, 1.0), (1.0, 20, 0.5), (0.9, 1024, 1.0)]
+    params = [(0.0, 64, 0.95), (0.0, 64, 0.95), (0.7, 64, 0.95), (1.3, 1, 1.0), (1.0, 20, 0.5), (0.9, 1024, 1.0),
+              (1.1, 0, 0.9), (0.8, 0, 1.0), (1.0, 2000, 0.97), (2.0, 5000, 1.0)]     # the last four: sorted in global memory
+    logits = np.concatenate([logits, (rng.standard_normal((4, vocab)) * 3).astype(np.float32)])
+    logits[7, 5:400:7] = logits[7].max()                               # many equal maxima among all tokens
     dev = torch.from_numpy(logits).cuda()
-    out = torch.empty(6, dtype=torch.int32, device="cuda")
+    out = torch.empty(len(params), dtype=torch.int32, device="cuda")
     for trial in range(20):
         samplers = [plain.Sampler(t, k, p, seed=trial * 7 + i + 1) for i, (t, k, p) in enumerate(params)]
         us = []
@@ -98,7 +101,7 @@ def test_device_sampler_matches_the_plain_sampler():
                        torch.tensor([p[0] for p in params], dtype=torch.float32, device="cuda"),
                        torch.tensor([p[1] for p in params], dtype=torch.int32, device="cuda"),
                        torch.tensor([p[2] for p in params], dtype=torch.float32, device="cuda"),
-                       torch.tensor(us, dtype=torch.float32, device="cuda"))
+                       torch.tensor(us, dtype=torch.float32, device="cuda"), wide=True)
         got = out.tolist()
         want = [s.sample(logits[i]) for i, s in enumerate(samplers)]
         assert got == want, f"trial {trial}: {got} != {want}"
@@ -121,8 +124,13 @@ def test_temperature_sampling_is_seeded(model_folders):
     for i, (p, r) in enumerate(zip(prompts, a)):
         want, _ = plain.generate(pcfg, w, p, 10, temperature=0.8, top_k=50, top_p=0.9, seed=123 + i)
         assert r.tokens == want
+    # top_k = 0: every token is a candidate (src/sampler.rs:43-47)
+    sp0 = SamplingParams(temperature=1.1, top_k=0, top_p=0.9, seed=7)
+    for i, (p, r) in enumerate(zip(prompts, eng.generate(prompts, max_tokens=6, sampling=sp0, stop_ids=[]))):
+        want, _ = plain.generate(pcfg, w, p, 6, temperature=1.1, top_k=0, top_p=0.9, seed=7 + i)
+        assert r.tokens == want
     with pytest.raises(ValueError, match="top_k"):
-        eng.generate(prompts, sampling=SamplingParams(temperature=1.0, top_k=0))
+        eng.generate(prompts, sampling=SamplingParams(temperature=1.0, top_k=-1))
 
 
 def test_command_line(model_folders, tmp_path):
