@@ -366,7 +366,8 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
   __shared__ int span[3];                // pages before token t, through token t, of all tokens
   pdl_release_next();
   const int t = blockIdx.x / nkv, kvh = blockIdx.x % nkv;
-  if (ntok <= MERGE_COUNT_ITSELF) {
+  const bool early = ntok <= MERGE_COUNT_ITSELF;
+  if (early) {
     // with few tokens the CTA counts the pages itself, from the step's inputs, while the stream
     // kernel is still running; else it reads the stream kernel's list once that is done
     if (threadIdx.x < 32) {
@@ -393,8 +394,6 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
       }
       if (lane == 0) span[2] = carry;
     }
-    __syncthreads();
-    pdl_wait_prior();
   } else {
     pdl_wait_prior();
     if (threadIdx.x == 0) {
@@ -402,31 +401,48 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
       span[1] = prefix[t + 1];
       span[2] = prefix[ntok];
     }
-    __syncthreads();
   }
+  __syncthreads();
   const int rep = nh / nkv, W = HD + 2;
   const long long P = (long long)span[2] * nkv;
   const int pages = span[1] - span[0];
   const long long u0 = (long long)span[0] * nkv + (long long)kvh * pages, u1 = u0 + pages;
   const int first = (int)(((u0 + 1) * G - 1) / P), last = (int)((u1 * G - 1) / P);
-  if (first == last) return;
   const int n = last - first + 1, tid = threadIdx.x, nthr = blockDim.x;
-  if (tid < MAX_REP) {
-    run_m[tid] = -INFINITY;
-    run_l[tid] = 0.f;
-  }
-  float acc[MERGE_EPT];
-#pragma unroll
-  for (int e = 0; e < MERGE_EPT; ++e) acc[e] = 0.f;
-  for (int base = 0; base < n; base += MERGE_ROUND) {
-    const int cn = min(MERGE_ROUND, n - base);
-    __syncthreads();
+  // which scratch slot each part lies in: known from the page counts alone
+  auto slots_of_round = [&](int base, int cn) {
     if (tid < cn) {
       const long long j = first + base + tid, start = j * P / G;
       // a CTA's part of this (token, kv head) is its first segment if its range starts inside it
       slot_of[tid] = start == (j + 1) * P / G ? -1 : (int)j * 2 + (start >= u0 ? 0 : 1);
     }
+  };
+  if (tid < MAX_REP) {
+    run_m[tid] = -INFINITY;
+    run_l[tid] = 0.f;
+  }
+  if (n > 1) slots_of_round(0, min(MERGE_ROUND, n));
+  if (early) pdl_wait_prior();   // every CTA waits, also one with nothing to add: the kernel after this one relies on it
+  if (n == 1) return;
+  float acc[MERGE_EPT];
+#pragma unroll
+  for (int e = 0; e < MERGE_EPT; ++e) acc[e] = 0.f;
+  constexpr int AHEAD = 8;   // parts of the thread's first value asked for before the factors are known
+  for (int base = 0; base < n; base += MERGE_ROUND) {
+    const int cn = min(MERGE_ROUND, n - base);
     __syncthreads();
+    if (base > 0) slots_of_round(base, cn);
+    __syncthreads();
+    float ahead[AHEAD];
+    {
+      const int rr = tid / HD, d = tid % HD;
+      const float* src = part + (size_t)rr * W + d;
+#pragma unroll
+      for (int jj = 0; jj < AHEAD; ++jj) {
+        const int sl = jj < cn ? slot_of[jj] : -1;
+        ahead[jj] = (sl >= 0 && tid < rep * HD) ? src[(size_t)sl * rep * W] : 0.f;
+      }
+    }
     for (int i = tid; i < cn * rep; i += nthr) {
       const int jj = i / rep, rr = i % rep, sl = slot_of[jj];
       const float* src = part + ((size_t)max(sl, 0) * rep + rr) * W;
@@ -456,8 +472,14 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
         const int rr = i / HD, d = i % HD;
         const float* src = part + (size_t)rr * W + d;
         float a = acc[e] * scale[rr];
+        int jj = 0;
+        if (e == 0) {
+#pragma unroll
+          for (; jj < AHEAD; ++jj)
+            if (jj < cn) a += fac[jj][rr] * ahead[jj];   // 0 where the slot is empty
+        }
 #pragma unroll 8
-        for (int jj = 0; jj < cn; ++jj) {
+        for (; jj < cn; ++jj) {
           const int sl = slot_of[jj];
           if (sl >= 0) a += fac[jj][rr] * src[(size_t)sl * rep * W];
         }

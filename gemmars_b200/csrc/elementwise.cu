@@ -120,7 +120,8 @@ GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtyp
 //   k heads: optional RMSNorm (weight kw), optional rotation; written back in place and, with
 //            FLAG_CACHE, into the paged key cache.
 //   v heads: with FLAG_CACHE copied into the paged value cache (transposed inside the page).
-enum { FLAG_NORM = 1, FLAG_ROPE = 2, FLAG_CACHE = 4, FLAG_INPLACE = 8, FLAG_V_TILED = 16 };
+//   FLAG_SINGLE: the tokens are single positions of different sequences (a decode step).
+enum { FLAG_NORM = 1, FLAG_ROPE = 2, FLAG_CACHE = 4, FLAG_INPLACE = 8, FLAG_V_TILED = 16, FLAG_SINGLE = 32 };
 
 // One head of one token, by one warp.  cs / sn: cos and sin of the token's angles (rot / 2 each).
 template <typename T>
@@ -311,7 +312,9 @@ GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, in
   if ((flags & FLAG_NORM) && (!qw || !kw)) return GB_ERR_ARG;
   if ((flags & FLAG_ROPE) && !inv_freq) return GB_ERR_ARG;
   PagedKV kv{page_table, table_width, page_size, nkv, hd};
-  const bool v_tiled = (flags & FLAG_CACHE) && nkv > 0 && ntok >= 64;   // prompts: values through the transposing kernel
+  // prompts: values through the transposing kernel (FLAG_SINGLE: every token is a single position
+  // of another sequence, where that kernel would gather nothing)
+  const bool v_tiled = (flags & FLAG_CACHE) && !(flags & FLAG_SINGLE) && nkv > 0 && ntok >= 64;
   if (v_tiled) flags |= FLAG_V_TILED;
   const int heads = nh + 2 * nkv;
   const int threads = heads >= 8 ? 256 : 32 * heads;

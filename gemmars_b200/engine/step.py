@@ -14,6 +14,7 @@ that start together and the requested rows are this engine's own.
 from __future__ import annotations
 
 import dataclasses
+import gc
 from typing import Optional, Sequence
 
 import numpy as np
@@ -284,8 +285,18 @@ class _DecodeGraph:
             torch.cuda.synchronize(dev)
             before = kernels.launch_count()
             self.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(self.graph, pool=runner._graph_pool()):
-                self.logits = self._forward()
+            # No graph of an earlier runner may be destroyed while this one is being captured (its
+            # destructor frees device memory, which ends the capture with an error): collect what
+            # is garbage now, and keep the collector from running inside the capture.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(self.graph, pool=runner._graph_pool()):
+                    self.logits = self._forward()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             self.launches = kernels.launch_count() - before
         finally:
             build.set_pdl(False)

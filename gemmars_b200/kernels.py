@@ -16,7 +16,7 @@ from .csrc import build
 
 F32, BF16 = 0, 1
 OUT_STORE, OUT_ACCUMULATE = 0, 1
-FLAG_NORM, FLAG_ROPE, FLAG_CACHE, FLAG_INPLACE = 1, 2, 4, 8
+FLAG_NORM, FLAG_ROPE, FLAG_CACHE, FLAG_INPLACE, FLAG_SINGLE = 1, 2, 4, 8, 32
 MAX_TOP_K = 1024
 
 _ERRORS = {-2: "unsupported element type", -3: "unsupported size", -4: "missing argument"}
@@ -168,7 +168,7 @@ def head_norm_rope_cache(qkv, nh, nkv, hd, rot, q_weight, k_weight, eps, inv_fre
              eps, _ptr(inv_freq), q_scale, tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(),
              _ptr(page_table), page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache),
              _ptr(vcache), flags, _stream()), "head_norm_rope_cache")
-    if (flags & FLAG_CACHE) and nkv > 0 and qkv.shape[0] >= 64:
+    if (flags & FLAG_CACHE) and not (flags & FLAG_SINGLE) and nkv > 0 and qkv.shape[0] >= 64:
         count_launches(1)   # prompts: the values go through a second, transposing kernel
 
 

@@ -93,6 +93,8 @@ class Attention(Part):
         qkv = self.qkv(h)
         norm = kernels.FLAG_NORM if self.qk_norm else 0
         store = kernels.FLAG_CACHE if writes_cache else 0
+        if ctx.max_new <= 1:
+            store |= kernels.FLAG_SINGLE       # a decode step: one position of each sequence
         common = (ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, group.page_table, group.page_size,
                   kc if writes_cache else None, vc if writes_cache else None)
         if self.position is None or isinstance(self.position, Rotary):
