@@ -100,12 +100,63 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = from_f32<T>(row[i] * inv * w[i]);
 }
 
+// Many rows (a prompt), bfloat16 out: one warp per row, no block barrier.  The row is read twice
+// (the second time from L1) with eight 16-byte loads of a lane in flight, which is what the
+// kernel lives on when there are thousands of rows; the float32 engine keeps the kernel above
+// for every number of rows, since the block's shape fixes the order of the additions.
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           bf16* __restrict__ out, const int* __restrict__ rows_index,
+                                                           int rows, int n, float eps) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const float4* row4 = (const float4*)(x + (size_t)(rows_index ? rows_index[r] : r) * n);
+  const float4* w4 = (const float4*)w;
+  const int n4 = n / 4;
+  float ss = 0.f;
+  for (int base = 0; base < n4; base += 32 * 8) {
+    float4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + lane + 32 * u;
+      v[u] = i < n4 ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+  uint2* o = (uint2*)(out + (size_t)r * n);
+  for (int base = 0; base < n4; base += 32 * 8) {
+    float4 v[8], g[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + lane + 32 * u;
+      if (i < n4) {
+        v[u] = row4[i];
+        g[u] = w4[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + lane + 32 * u;
+      if (i < n4) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * inv * g[u].x, v[u].y * inv * g[u].y);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * inv * g[u].z, v[u].w * inv * g[u].w);
+        o[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+      }
+    }
+  }
+}
+
 GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
                          int n, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
   const int threads = n >= 1024 ? 256 : 128;
   if (out_dtype == GB_F32)
     gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps);
+  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0)
+    gb_launch(rmsnorm_rows_kernel, (rows + 7) / 8, 256, 0, stream, x, w, (bf16*)out, rows_index, rows, n, eps);
   else if (out_dtype == GB_BF16)
     gb_launch(rmsnorm_kernel<bf16>, rows, threads, 0, stream, x, w, (bf16*)out, rows_index, n, eps);
   else
@@ -238,6 +289,103 @@ __device__ __forceinline__ void head_norm_rope_cache_one(T* __restrict__ qkv, in
   }
 }
 
+// Prompts, bfloat16, all dims rotated, head size 16 * 2^j: a head is taken by hd / 16 lanes, each
+// with 8 adjacent dims of either half (16-byte loads and stores), so a warp takes 32 / (hd / 16)
+// heads at once and a token's query and key heads are a dozen warp tasks instead of forty.  One
+// CTA per token, a warp per task.  Value heads are not touched here.
+template <int LANES>   // lanes per head = hd / 16
+__global__ void __launch_bounds__(320, 3) head_norm_rope_cache_wide_kernel(bf16* __restrict__ qkv, int ntok, int nh, int nkv, int hd,
+                                                 const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                                 const float* __restrict__ inv_freq, float q_scale,
+                                                 const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                                 const int* __restrict__ seq_slot, PagedKV kv,
+                                                 bf16* __restrict__ kcache, int flags) {
+  extern __shared__ float trig[];   // cos [hd / 2], sin [hd / 2]
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x, half = hd / 2;
+  const int pos = tok_pos[t];
+  float* cs = trig;
+  float* sn = trig + half;
+  int page = 0;   // needed for the key heads' stores only: its loads run under the heads' loads
+  if (flags & FLAG_CACHE)
+    page = kv.page_table[(size_t)seq_slot[tok_seq[t]] * kv.table_width + (pos / kv.page_size) % kv.table_width];
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+  __syncthreads();
+  constexpr int HEADS = 32 / LANES;
+  const int lane = threadIdx.x & 31, sub = lane % LANES, which = lane / LANES;
+  const int heads = nh + 2 * nkv, qk = nh + nkv;
+  for (int h0 = (threadIdx.x >> 5) * HEADS; h0 < qk; h0 += (blockDim.x >> 5) * HEADS) {
+    const int h = h0 + which;
+    const bool live = h < qk;
+    const bool is_q = h < nh;
+    bf16* src = qkv + ((size_t)t * heads + (live ? h : 0)) * hd;
+    const int i = 8 * sub;   // this lane: dims i .. i + 7 and i + half .. i + half + 7
+    uint4 ra = make_uint4(0, 0, 0, 0), rb = ra;
+    if (live) {
+      ra = *(const uint4*)(src + i);
+      rb = *(const uint4*)(src + i + half);
+    }
+    const float* w = is_q ? qw : kw;
+    float wa[8], wb[8], a[8], b[8];
+    if ((flags & FLAG_NORM) && live) {
+      *(float4*)&wa[0] = *(const float4*)(w + i);
+      *(float4*)&wa[4] = *(const float4*)(w + i + 4);
+      *(float4*)&wb[0] = *(const float4*)(w + i + half);
+      *(float4*)&wb[4] = *(const float4*)(w + i + half + 4);
+    }
+    const __nv_bfloat162* pa = (const __nv_bfloat162*)&ra;
+    const __nv_bfloat162* pb = (const __nv_bfloat162*)&rb;
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+      a[2 * j] = fa.x; a[2 * j + 1] = fa.y; b[2 * j] = fb.x; b[2 * j + 1] = fb.y;
+      ss += fa.x * fa.x + fa.y * fa.y + fb.x * fb.x + fb.y * fb.y;
+    }
+    float inv = 1.f;
+    if (flags & FLAG_NORM) {
+#pragma unroll
+      for (int o = 1; o < LANES; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      inv = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    if (!live) continue;
+    const float scale = is_q ? q_scale : 1.f;
+    float c[8], sgn[8];
+    *(float4*)&c[0] = *(const float4*)(cs + i);
+    *(float4*)&c[4] = *(const float4*)(cs + i + 4);
+    *(float4*)&sgn[0] = *(const float4*)(sn + i);
+    *(float4*)&sgn[4] = *(const float4*)(sn + i + 4);
+    uint4 oa, ob;
+    __nv_bfloat162* qa = (__nv_bfloat162*)&oa;
+    __nv_bfloat162* qb = (__nv_bfloat162*)&ob;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float lo[2], hi[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int d = 2 * j + e;
+        float x = a[d] * inv, y = b[d] * inv;
+        if (flags & FLAG_NORM) {
+          x *= wa[d];
+          y *= wb[d];
+        }
+        lo[e] = (x * c[d] - y * sgn[d]) * scale;
+        hi[e] = (y * c[d] + x * sgn[d]) * scale;
+      }
+      qa[j] = __floats2bfloat162_rn(lo[0], lo[1]);
+      qb[j] = __floats2bfloat162_rn(hi[0], hi[1]);
+    }
+    *(uint4*)(src + i) = oa;
+    *(uint4*)(src + i + half) = ob;
+    if (!is_q && (flags & FLAG_CACHE)) {
+      bf16* cdst = kcache + (((size_t)page * nkv + (h - nh)) * kv.page_size + pos % kv.page_size) * hd;
+      *(uint4*)(cdst + i) = oa;
+      *(uint4*)(cdst + i + half) = ob;
+    }
+  }
+}
+
 // A CTA takes `heads_per_cta` heads of one token (grid: tokens x groups of heads): the token's
 // rot / 2 angles (float32(position) * inv_freq, as the reference) and their cos and sin are computed
 // once into shared memory and the token's page is looked up once, while the heads' loads are already
@@ -317,6 +465,30 @@ GB_EXPORT int gb_head_norm_rope_cache(void* qkv, int dtype, int ntok, int nh, in
   const bool v_tiled = (flags & FLAG_CACHE) && !(flags & FLAG_SINGLE) && nkv > 0 && ntok >= 64;
   if (v_tiled) flags |= FLAG_V_TILED;
   const int heads = nh + 2 * nkv;
+  const int lanes = hd / 16;
+  if (v_tiled && dtype == GB_BF16 && (flags & FLAG_ROPE) && (flags & FLAG_INPLACE) && rot == hd && hd % 16 == 0 &&
+      (lanes & (lanes - 1)) == 0 && lanes <= 16 && (((uintptr_t)qkv | (uintptr_t)kcache) & 15) == 0) {
+    const int tasks = ((nh + nkv) * lanes + 31) / 32;
+    const int threads = 32 * (tasks < 10 ? tasks : 10);   // 10 warps: three CTAs share an SM
+    const size_t trig_bytes = (size_t)hd * sizeof(float);
+#define GB_WIDE(L) \
+  gb_launch(head_norm_rope_cache_wide_kernel<L>, ntok, threads, trig_bytes, stream, (bf16*)qkv, ntok, nh, nkv, hd, qw, kw, eps, \
+            inv_freq, q_scale, tok_pos, tok_seq, seq_slot, kv, (bf16*)kcache, flags)
+    switch (lanes) {
+      case 1: GB_WIDE(1); break;
+      case 2: GB_WIDE(2); break;
+      case 4: GB_WIDE(4); break;
+      case 8: GB_WIDE(8); break;
+      default: GB_WIDE(16); break;
+    }
+#undef GB_WIDE
+    int rc = gb_launch_status();
+    if (rc != 0) return rc;
+    dim3 vgrid((ntok + 31) / 32, nkv);
+    gb_launch(value_cache_tile_kernel<bf16>, vgrid, 128, (size_t)32 * (hd + 2) * 2, stream, (const bf16*)qkv, ntok, nh, nkv,
+              hd, tok_pos, tok_seq, seq_slot, kv, (bf16*)vcache);
+    return gb_launch_status();
+  }
   const int threads = heads >= 8 ? 256 : 32 * heads;
   const int heads_per_cta = ntok >= 64 ? heads : threads / 32;
   const dim3 grid(ntok, (heads + heads_per_cta - 1) / heads_per_cta);

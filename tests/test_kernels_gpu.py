@@ -147,17 +147,27 @@ def test_embedding_and_gated_activation(k):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hd,rot,nh,nkv", [(48, 24, 5, 1), (16, 16, 4, 2), (128, 128, 8, 2)])
-def test_head_norm_rope_cache(k, dtype, hd, rot, nh, nkv):
+@pytest.mark.parametrize("step", ["few", "prompt"])
+@pytest.mark.parametrize("hd,rot,nh,nkv", [(48, 24, 5, 1), (16, 16, 4, 2), (128, 128, 8, 2), (64, 64, 7, 1), (32, 32, 3, 3),
+                                            (256, 256, 2, 1), (96, 96, 2, 2)])
+def test_head_norm_rope_cache(k, dtype, step, hd, rot, nh, nkv):
+    """A step of a few tokens (one warp per head) and one of prompt size (64 tokens and more: in
+    bfloat16 the kernel with several heads to a warp, and the values through the tile kernel)."""
     torch.manual_seed(hd)
-    lengths = [70, 5]
+    if step == "few":
+        lengths = [70, 5]
+        # sequence 0 appends positions 66..69, sequence 1 positions 0..4
+        seqs, poss = [0] * 4 + [1] * 5, [66, 67, 68, 69, 0, 1, 2, 3, 4]
+    else:
+        lengths = [150, 37]
+        # sequence 0 appends positions 60..149 (across page borders), sequence 1 its whole prompt
+        seqs, poss = [0] * 90 + [1] * 37, list(range(60, 150)) + list(range(37))
     kc, vc, table, _ = _paged(2, lengths, nkv, hd, dtype)
     kc.zero_(); vc.zero_()
-    # the step: sequence 0 appends positions 66..69, sequence 1 positions 0..4
-    tok_seq = torch.tensor([0] * 4 + [1] * 5, dtype=torch.int32, device="cuda")
-    tok_pos = torch.tensor([66, 67, 68, 69, 0, 1, 2, 3, 4], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor(seqs, dtype=torch.int32, device="cuda")
+    tok_pos = torch.tensor(poss, dtype=torch.int32, device="cuda")
     seq_slot = torch.tensor([0, 1], dtype=torch.int32, device="cuda")
-    t = 9
+    t = len(seqs)
     qkv = torch.randn(t, (nh + 2 * nkv) * hd, device="cuda").to(dtype)
     qw, kw = torch.rand(hd, device="cuda") + 0.5, torch.rand(hd, device="cuda") + 0.5
     theta, eps, scale = 5e4, 1e-5, hd ** -0.5
