@@ -40,17 +40,19 @@ PREFILL_TOKENS = 2048
 
 
 def peaks():
+    """(copy GB/s, bf16 TFLOP/s as a burst, bf16 TFLOP/s sustained under the power cap, where from)."""
     path = os.path.join(HERE, "MEASURED_PEAKS.json")
-    hbm, tf, src = 6650.0, 1590.0, "fallback"
+    hbm, tf, tf_sustained, src = 6650.0, 1590.0, 1400.0, "fallback"
     try:
         with open(path) as f:
             p = json.load(f)
         hbm = float(p.get("hbm_gbs", hbm))
         tf = float(p.get("bf16_tflops", tf))
+        tf_sustained = float(p.get("bf16_tflops_sustained", min(tf, tf_sustained)))
         src = "measured"
     except (OSError, ValueError):
         pass
-    return hbm, tf, src
+    return hbm, tf, tf_sustained, src
 
 
 class ClockSampler:
@@ -197,7 +199,7 @@ def main():
     from gemmars_b200.sampling.sampler import BatchSampler, SamplingParams
     from gemmars_b200.weights.random_init import random_weights
 
-    hbm_gbs, tflops, peak_src = peaks()
+    hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
     cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
     vocab = cfg["vocab_size"]
     torch.cuda.set_device(0)
@@ -212,6 +214,23 @@ def main():
     eng = Engine.from_config(cfg, tensors, opts)
     del tensors
     runner, model = eng.runner, eng.model
+
+    # ---- prefill of 2,048 tokens (first: a prompt is a burst of work on a GPU that was waiting)
+    toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(3)).tolist()
+    pre_ms = []
+    for it in range(10):
+        s = runner.open()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepItem(s, toks, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:                        # three warm-up prompts
+            pre_ms.append(e0.elapsed_time(e1))
+        runner.close(s)
+    pre = statistics.median(pre_ms)
+    pre_frac = prefill_flops(cfg, args.layers, PREFILL_TOKENS) / (pre / 1e3) / (tflops * 1e12)
 
     # ---- the timed decode steps (device time, CUDA events)
     clocks = ClockSampler()
@@ -233,23 +252,6 @@ def main():
     e2e_value = st.generated_tokens / max(st.decode_secs, 1e-9)
     h2d = (8 * args.batch + 1) * 4
     d2h = args.batch * 4
-
-    # ---- prefill of 2,048 tokens
-    toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=gen).tolist()
-    pre_ms = []
-    for it in range(8):
-        s = runner.open()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        runner.step([StepItem(s, toks, [PREFILL_TOKENS - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        if it:
-            pre_ms.append(e0.elapsed_time(e1))
-        runner.close(s)
-    pre = statistics.median(pre_ms)
-    pre_frac = prefill_flops(cfg, args.layers, PREFILL_TOKENS) / (pre / 1e3) / (tflops * 1e12)
 
     pts = {}
     if points:
@@ -278,7 +280,9 @@ def main():
                 "prefill_secs": round(st.prefill_secs, 3)},
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / (pre / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre, 3),
-                    "frac": round(pre_frac, 4)},
+                    "frac": round(pre_frac, 4),
+                    # the prompt is a 30 ms run of products under the power cap: also against the sustained rate
+                    "frac_sustained": round(pre_frac * tflops / tflops_sustained, 4)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
                      "frac": round(achieved / hbm_gbs, 4), "bytes_per_step": step_bytes},
         "points": pts,

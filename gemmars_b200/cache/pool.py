@@ -178,11 +178,14 @@ class KVGroup:
             return
         rows = sorted(self._dirty)
         self._dirty.clear()
-        if len(rows) * 4 >= self.table_host.shape[0]:
+        # The host table is ordinary (pageable) memory on purpose: a copy from it is staged when it
+        # is asked for, so later changes of the host table (the next step's pages, a slot given
+        # back) cannot reach a copy that the device has not run yet.
+        if len(rows) > 4:
             self.page_table.copy_(self.table_host)
         else:
-            idx = torch.tensor(rows, dtype=torch.long)
-            self.page_table[idx.to(self.page_table.device)] = self.table_host[idx].to(self.page_table.device)
+            for r in rows:
+                self.page_table[r].copy_(self.table_host[r])
 
     def layer(self, i: int):
         """(k, v) storage of the group's ``i``-th layer: k ``[pages + 1, kv_heads, page_size, head_dim]``,

@@ -39,7 +39,9 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of the current stream of the current device (what
+    # torch.cuda.current_stream().cuda_stream gives, without building a Stream object per launch)
+    return torch._C._cuda_getCurrentRawStream(torch.cuda.current_device())
 
 
 _launches = [0]
