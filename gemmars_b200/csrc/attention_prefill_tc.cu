@@ -32,6 +32,7 @@ constexpr uint32_t SMEM_TILES = Q_BYTES + 2 * K_BYTES + 2 * V_BYTES + P_BYTES;
 constexpr uint32_t TMEM_COLS = 256, S_COL0 = 0, S_COL1 = 64, O_COL = 128;
 constexpr uint32_t IDESC_S = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(KEYS >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 constexpr uint32_t IDESC_PV = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+constexpr float RESCALE_STEP = 8.0f;   // how far a row's maximum may outgrow its reference before O is rescaled
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ int g_attn_status;   // 0, or the barrier whose wait ran out first (1..6)
@@ -73,12 +74,25 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
+#ifdef GB_TRACE
+__device__ long long g_attn_trace[64 * 16];
+#define ATRACE(j, slot) do { if (traced && (j) < 64) g_attn_trace[(j) * 16 + (slot)] = clock64(); } while (0)
+#else
+#define ATRACE(j, slot)
+#endif
+
+__device__ __forceinline__ float ex2(float x) {   // 2^x, one instruction; 2^-inf = 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *(uint32_t*)&v;
 }
 
-// grid (token tiles upper bound, query heads); block 192: warps 0-3 softmax, 4 TMA, 5 MMA.
+// grid (query heads, token tiles upper bound); block 192: warps 0-3 softmax, 4 TMA, 5 MMA.
 __global__ void __launch_bounds__(192, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, long long out_stride,
@@ -92,18 +106,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* p_smem = v_smem + 2 * V_BYTES;
   uint64_t* bars = (uint64_t*)(smem + SMEM_TILES);
   uint64_t* q_full = bars;            // 1
-  uint64_t* kv_full = bars + 1;       // 2
-  uint64_t* kv_empty = bars + 3;      // 2
-  uint64_t* s_full = bars + 5;        // 2
-  uint64_t* s_empty = bars + 7;       // 2
-  uint64_t* p_full = bars + 9;        // 1
-  uint64_t* o_done = bars + 10;       // 1
-  uint32_t* tmem_slot = (uint32_t*)(bars + 11);
+  uint64_t* k_full = bars + 1;        // 2: a page of keys has arrived
+  uint64_t* k_empty = bars + 3;       // 2: the S product that read it is done
+  uint64_t* v_full = bars + 5;        // 2: a page of values has arrived
+  uint64_t* v_empty = bars + 7;       // 2: the P V product that read it is done
+  uint64_t* s_full = bars + 9;        // 2
+  uint64_t* s_empty = bars + 11;      // 2
+  uint64_t* p_full = bars + 13;       // 1
+  uint64_t* o_done = bars + 14;       // 1
+  uint32_t* tmem_slot = (uint32_t*)(bars + 15);
   volatile int* abort = (volatile int*)(tmem_slot + 1);
 
   pdl_wait_prior();
-  // ---- which sequence and which 128-token tile of it
-  int b = 0, tile = blockIdx.x;
+  // ---- which sequence and which 128-token tile of it.  The grid is (heads, tiles) and the tiles are
+  // taken from the last down: a causal tile's work grows with its place in the sequence (2 to 34
+  // pages in a 2,048-token prompt), and CTAs start in the order of the grid, so the long ones of
+  // all heads go first and the short ones fill the end of the kernel.
+  int b = 0, tile = gridDim.y - 1 - blockIdx.y;
   for (; b < n_seqs; ++b) {
     const int tiles = (cu_seqlens[b + 1] - cu_seqlens[b] + ROWS - 1) / ROWS;
     if (tile < tiles) break;
@@ -111,7 +130,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   }
   if (b >= n_seqs) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int head = blockIdx.y, kvh = head / (nh / nkv);
+  const int head = blockIdx.x, kvh = head / (nh / nkv);
   const int seq_len = cu_seqlens[b + 1] - cu_seqlens[b];
   const int first = tile * ROWS;
   const int rows_valid = min(ROWS, seq_len - first);
@@ -120,6 +139,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int pos_last = start + first + rows_valid - 1;
   const int lo_first = window > 0 ? max(0, start + first + 1 - window) : 0;
   const int kt_begin = lo_first / KEYS, n_tiles = pos_last / KEYS + 1 - kt_begin;
+#ifdef GB_TRACE
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 1 && (threadIdx.x & 31) == 0;   // one long tile of head 0
+#endif
 
   if (threadIdx.x == 0) {
     if (smem_u32(smem) & 1023u) {   // the swizzled tiles need 1024-byte alignment
@@ -130,8 +152,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     }
     mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], 4);
     }
@@ -156,50 +180,92 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
       mbar_expect_tx(q_full, Q_BYTES);
       for (int h = 0; h < QH; ++h) tma_load_2d(q_smem + h * (ROWS * 128), &map_q, head * HD + h * 64, tok0, q_full);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !wait_or_abort(&kv_empty[s], ((j >> 1) - 1) & 1, abort, 1)) break;
-        const int page = page_table[(size_t)slot * table_width + (kt_begin + j) % table_width];
-        const int row = page * nkv + kvh;
-        mbar_expect_tx(&kv_full[s], K_BYTES + V_BYTES);
-        for (int h = 0; h < QH; ++h)
-          tma_load_2d(k_smem + s * K_BYTES + h * (KEYS * 128), &map_k, h * 64, row * KEYS, &kv_full[s]);
-        tma_load_2d(v_smem + s * V_BYTES, &map_v, 0, row * HD, &kv_full[s]);
+      // Keys and values have stages and barriers of their own: a stage of keys is free as soon as
+      // the S product that read it is done, long before the P V product frees the values of the same
+      // page, so the keys of page j + 2 are on their way while page j is still being worked on
+      // (with one barrier for both, the next S product waited a full round trip to memory behind
+      // every P V product: 3,400 cycles a page against 640 of MMAs).  The thread takes whichever
+      // load can go next.
+      int jk = 0, jv = 0;
+      uint32_t spins = 0;
+      while ((jk < n_tiles || jv < n_tiles) && !*abort) {
+        bool moved = false;
+        if (jk < n_tiles && (jk < 2 || mbar_try_wait(&k_empty[jk & 1], ((jk >> 1) - 1) & 1))) {
+          const int sidx = jk & 1;
+          ATRACE(jk, 0);   // producer: keys' stage free, about to load page jk
+          const int page = page_table[(size_t)slot * table_width + (kt_begin + jk) % table_width];
+          const int row = page * nkv + kvh;
+          mbar_expect_tx(&k_full[sidx], K_BYTES);
+          for (int h = 0; h < QH; ++h)
+            tma_load_2d(k_smem + sidx * K_BYTES + h * (KEYS * 128), &map_k, h * 64, row * KEYS, &k_full[sidx]);
+          ++jk;
+          moved = true;
+        }
+        if (jv < n_tiles && jv < jk && (jv < 2 || mbar_try_wait(&v_empty[jv & 1], ((jv >> 1) - 1) & 1))) {
+          const int sidx = jv & 1;
+          const int page = page_table[(size_t)slot * table_width + (kt_begin + jv) % table_width];
+          const int row = page * nkv + kvh;
+          mbar_expect_tx(&v_full[sidx], V_BYTES);
+          tma_load_2d(v_smem + sidx * V_BYTES, &map_v, 0, row * HD, &v_full[sidx]);
+          ++jv;
+          moved = true;
+        }
+        if (moved) {
+          spins = 0;
+        } else if (++spins > WAIT_LIMIT) {
+          *abort = 1;
+          atomicCAS(&g_attn_status, 0, 1);
+          break;
+        }
       }
     }
     if (lane == 0) pdl_release_next();   // the last page is on its way: the next kernel may move in
     __syncwarp();
   } else if (warp == 5) {
-    // ---------------- MMA issue: S one page ahead of the softmax, then O += P V
-    if (lane == 0 && !*abort) {
-      bool ok = wait_or_abort(q_full, 0, abort, 2);
-      auto issue_s = [&](int t) -> bool {
-        const int s = t & 1;
-        if (!wait_or_abort(&kv_full[s], (t >> 1) & 1, abort, 3)) return false;
-        if (t >= 2 && !wait_or_abort(&s_empty[s], ((t >> 1) - 1) & 1, abort, 4)) return false;
-        tc_fence_after();
-        const uint32_t d = tmem + (s ? S_COL1 : S_COL0);
+    // ---------------- MMA issue: S up to two pages ahead of the softmax, and O += P V as soon as a
+    // P is there; whichever can go next (neither waits for the other's operands)
+    if (lane == 0 && !*abort && wait_or_abort(q_full, 0, abort, 2)) {
+      int js = 0, jp = 0;   // next S, next P V
+      uint32_t spins = 0;
+      while (jp < n_tiles && !*abort) {
+        bool moved = false;
+        if (js < n_tiles && mbar_try_wait(&k_full[js & 1], (js >> 1) & 1) &&
+            (js < 2 || mbar_try_wait(&s_empty[js & 1], ((js >> 1) - 1) & 1))) {
+          const int sidx = js & 1;
+          ATRACE(js, 2);   // MMA: keys here and S buffer free, issuing S
+          tc_fence_after();
+          const uint32_t d = tmem + (sidx ? S_COL1 : S_COL0);
 #pragma unroll
-        for (int h = 0; h < QH; ++h) {
-          const uint64_t qd = smem_desc(smem_u32(q_smem + h * (ROWS * 128)));
-          const uint64_t kd = smem_desc(smem_u32(k_smem + s * K_BYTES + h * (KEYS * 128)));
+          for (int h = 0; h < QH; ++h) {
+            const uint64_t qd = smem_desc(smem_u32(q_smem + h * (ROWS * 128)));
+            const uint64_t kd = smem_desc(smem_u32(k_smem + sidx * K_BYTES + h * (KEYS * 128)));
 #pragma unroll
-          for (int k = 0; k < 4; ++k) tc_mma(d, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), IDESC_S, (h > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) tc_mma(d, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), IDESC_S, (h > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&s_full[sidx]);
+          tc_commit(&k_empty[sidx]);
+          ++js;
+          moved = true;
         }
-        tc_commit(&s_full[s]);
-        return true;
-      };
-      ok = ok && issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles && !issue_s(j + 1)) break;
-        if (!wait_or_abort(p_full, j & 1, abort, 5)) break;
-        tc_fence_after();
-        const uint64_t pd = smem_desc(smem_u32(p_smem));
-        const uint64_t vd = smem_desc(smem_u32(v_smem + (j & 1) * V_BYTES));
+        if (jp < js && mbar_try_wait(p_full, jp & 1) && mbar_try_wait(&v_full[jp & 1], (jp >> 1) & 1)) {
+          ATRACE(jp, 3);   // MMA: P and the values are there, issuing P V
+          tc_fence_after();
+          const uint64_t pd = smem_desc(smem_u32(p_smem));
+          const uint64_t vd = smem_desc(smem_u32(v_smem + (jp & 1) * V_BYTES));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) tc_mma(tmem + O_COL, pd + (uint64_t)(k * 2), vd + (uint64_t)(k * 2), IDESC_PV, (j > 0 || k > 0) ? 1u : 0u);
-        tc_commit(o_done);
-        tc_commit(&kv_empty[j & 1]);
+          for (int k = 0; k < 4; ++k) tc_mma(tmem + O_COL, pd + (uint64_t)(k * 2), vd + (uint64_t)(k * 2), IDESC_PV, (jp > 0 || k > 0) ? 1u : 0u);
+          tc_commit(o_done);
+          tc_commit(&v_empty[jp & 1]);
+          ++jp;
+          moved = true;
+        }
+        if (moved) {
+          spins = 0;
+        } else if (++spins > WAIT_LIMIT) {
+          *abort = 1;
+          atomicCAS(&g_attn_status, 0, 3);
+          break;
+        }
       }
     }
     __syncwarp();
@@ -214,8 +280,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     bool ok = !*abort;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int sb = j & 1;
+      if (warp == 0) ATRACE(j, 4);   // softmax warp 0: starts to wait for S_j
       ok = __all_sync(0xffffffffu, wait_or_abort(&s_full[sb], (j >> 1) & 1, abort, 6));
       if (!ok) break;
+      if (warp == 0) ATRACE(j, 5);   // softmax warp 0: S_j seen
       tc_fence_after();
       uint32_t sv[64];
       tc_ld32(lane_addr + (sb ? S_COL1 : S_COL0), sv);
@@ -225,32 +293,54 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);     // this warp has its rows of S: the buffer may be written again
       const int key0 = (kt_begin + j) * KEYS;
-      float mx = -INFINITY;
+      // Only the pages on the diagonal and at a window's lower edge hold keys that a row must not
+      // see; the others skip the two comparisons and the select per score (the loop is bound by
+      // the number of instructions the four softmax warps issue, not by the exponentials).
+      if (__any_sync(0xffffffffu, key0 + KEYS - 1 > pos || key0 < lo)) {
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int key = key0 + c;
-        const float v = (key >= lo && key <= pos) ? __uint_as_float(sv[c]) * LOG2E : -INFINITY;
-        sv[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int c = 0; c < 64; ++c) {
+          const int key = key0 + c;
+          if (!(key >= lo && key <= pos)) sv[c] = __float_as_uint(-INFINITY);
+        }
       }
-      const float m_new = fmaxf(m, mx);
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[c]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[c + 1]));
+        mx2 = fmaxf(mx2, __uint_as_float(sv[c + 2]));
+        mx3 = fmaxf(mx3, __uint_as_float(sv[c + 3]));
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * LOG2E;   // log2 units from here on
+      // m is the reference the exponentials are taken against, not always the running maximum: it
+      // moves only when the maximum has outgrown it by more than RESCALE_STEP (in log2 units), so
+      // that O, which would have to be rescaled with it, is left alone on most pages.  p can then
+      // be as large as 2^RESCALE_STEP, which bfloat16 and the float32 sums take without loss;
+      // numerator and denominator carry the same factor.
+      const float m_new = (m == -INFINITY || mx > m + RESCALE_STEP) ? fmaxf(m, mx) : m;
       const float u = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = exp2f(m - u);
       m = m_new;
-      float sum = 0.f;
+      float sum0 = 0.f, sum1 = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        const float a = exp2f(__uint_as_float(sv[2 * c]) - u), bq = exp2f(__uint_as_float(sv[2 * c + 1]) - u);
-        sum += a + bq;
+        // one multiply-add and one ex2 per score: 2^(s * log2(e) - reference); a masked score is
+        // -inf and gives 0
+        const float a = ex2(fmaf(__uint_as_float(sv[2 * c]), LOG2E, -u));
+        const float bq = ex2(fmaf(__uint_as_float(sv[2 * c + 1]), LOG2E, -u));
+        sum0 += a;
+        sum1 += bq;
         pk[c] = pack2(a, bq);
       }
-      l = l * alpha + sum;
+      l = l * alpha + (sum0 + sum1);
+      if (warp == 0) ATRACE(j, 6);   // softmax warp 0: exponentials done
       if (j > 0) {
         // O of the pages before is complete; bring it to the new maximum where that moved
         ok = __all_sync(0xffffffffu, wait_or_abort(o_done, (j - 1) & 1, abort, 6));
         if (!ok) break;
         tc_fence_after();
+        if (warp == 0) ATRACE(j, 7);   // softmax warp 0: PV_{j-1} seen done
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
           for (int c = 0; c < HD; c += 32) {
@@ -273,6 +363,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
+      if (warp == 0) ATRACE(j, 8);   // softmax warp 0: P_j written
+      if (warp == 3) ATRACE(j, 9);   // softmax warp 3: P_j written
     }
     if (ok) ok = __all_sync(0xffffffffu, wait_or_abort(o_done, (n_tiles - 1) & 1, abort, 6));
     if (ok) {
@@ -324,20 +416,26 @@ GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, void* o
   if (!tensor_map(&mq, q, (uint64_t)ntok, (uint64_t)nh * HD, (uint64_t)q_stride * 2, ROWS)) return GB_ERR_ARG;
   if (!tensor_map(&mk, kcache, (uint64_t)pages * nkv * KEYS, (uint64_t)HD, (uint64_t)HD * 2, KEYS)) return GB_ERR_ARG;
   if (!tensor_map(&mv, vcache, (uint64_t)pages * nkv * HD, (uint64_t)KEYS, (uint64_t)KEYS * 2, HD)) return GB_ERR_ARG;
-  constexpr size_t SMEM = SMEM_TILES + 11 * 8 + 16;
+  constexpr size_t SMEM = SMEM_TILES + 15 * 8 + 16;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
       return (int)cudaGetLastError();
     configured = true;
   }
-  dim3 grid((ntok + ROWS - 1) / ROWS + n_seqs, nh);
+  dim3 grid(nh, (ntok + ROWS - 1) / ROWS + n_seqs);
   gb_launch(attention_prefill_tc_kernel, grid, 192, SMEM, stream, mq, mk, mv, (bf16*)out, out_stride, page_table,
             table_width, nkv, cu_seqlens, seq_start, seq_slot, n_seqs, nh, window);
   return gb_launch_status();
 }
 
 // 0, or the code of the first bounded wait that ran out (synchronizes the device).
+#ifdef GB_TRACE
+GB_EXPORT int gb_attention_prefill_tc_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(long long) * n);
+}
+#endif
+
 GB_EXPORT int gb_attention_prefill_tc_status(int reset) {
   int v = -1;
   if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof(int)) != cudaSuccess) return -1;
