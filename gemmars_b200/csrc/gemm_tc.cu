@@ -332,6 +332,13 @@ __device__ __forceinline__ void tile_origin(int t, int tiles_m, int tiles_n, int
   n0 = (r / gm) * BM;
 }
 
+#ifdef GB_TRACE
+__device__ long long g_ptrace[256 * 8];
+#define PTRACE(idx, slot) do { if (blockIdx.x == 0 && (idx) < 256) g_ptrace[(idx) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define PTRACE(idx, slot)
+#endif
+
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -395,6 +402,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             break;
           }
           uint8_t* a = smem + s * STAGE_BYTES;
+          PTRACE(it, 0);   // producer: stage free, loading block `it`
           mbar_expect_tx(&full_bar[s], stage_tx);
           tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
           if (DUAL) tma_load_2d(a + W_BYTES, &map_w, kb * BK, N + n0, &full_bar[s]);
@@ -425,6 +433,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             break;
           }
           tc_fence_after();
+          PTRACE(it, 1);   // MMA: block `it` has arrived
           const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES), udesc = smem_desc(a + W_BYTES);
 #pragma unroll
@@ -433,6 +442,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             if (DUAL) tc_mma(d + BN, udesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[s]);
+          PTRACE(it, 2);   // MMA: block `it` issued
         }
         tc_commit(&acc_full[b]);
       }
@@ -453,6 +463,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         break;
       }
       tc_fence_after();
+      if (threadIdx.x == 0) PTRACE(i, 3);   // epilogue: tile i complete
       const float bv = (bias && n < N) ? bias[n] : 0.f;
       const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16) + b * ACC_COLS;
 #pragma unroll 1
@@ -494,6 +505,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
+      if (threadIdx.x == 0) PTRACE(i, 4);   // epilogue: tile i stored
     }
   }
   tc_fence_before();
@@ -648,6 +660,9 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
 }
 
 #ifdef GB_TRACE
+GB_EXPORT int gb_gemm_tc_persistent_trace(long long* host, int n) {
+  return (int)cudaMemcpyFromSymbol(host, g_ptrace, sizeof(long long) * n);
+}
 GB_EXPORT int gb_gemm_tc_trace(unsigned long long* host, int n) {
   return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
 }
