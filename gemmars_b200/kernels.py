@@ -404,6 +404,7 @@ def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos,
 STREAM_DECODE_HEAD_DIMS = (64, 128)
 STREAM_DECODE_MAX_TOKENS = 4096
 _decode_stream_scratch = {}
+_outgrown = []
 
 
 def attention_decode_stream_usable(ntok: int, nh: int, nkv: int, hd: int, page_size: int) -> bool:
@@ -436,6 +437,8 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
     need = ctas * 2 * (nh // nkv) * (hd + 2) + ntok + 1
     scratch = _decode_stream_scratch.get(q.device.index)
     if scratch is None or scratch.numel() < need:
+        if scratch is not None:
+            _outgrown.append(scratch)     # a captured step may still point at it: never freed
         scratch = _decode_stream_scratch[q.device.index] = torch.empty(max(need, 1 << 20), dtype=torch.float32,
                                                                        device=q.device)
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
