@@ -302,7 +302,6 @@ __global__ void __launch_bounds__(320, 3) head_norm_rope_cache_wide_kernel(bf16*
                                                  bf16* __restrict__ kcache, int flags) {
   extern __shared__ float trig[];   // cos [hd / 2], sin [hd / 2]
   pdl_release_next();
-  pdl_wait_prior();
   const int t = blockIdx.x, half = hd / 2;
   const int pos = tok_pos[t];
   float* cs = trig;
@@ -312,6 +311,7 @@ __global__ void __launch_bounds__(320, 3) head_norm_rope_cache_wide_kernel(bf16*
     page = kv.page_table[(size_t)seq_slot[tok_seq[t]] * kv.table_width + (pos / kv.page_size) % kv.table_width];
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
   __syncthreads();
+  pdl_wait_prior();   // the angles and the page came from the step's inputs; q, k, v from the kernel before
   constexpr int HEADS = 32 / LANES;
   const int lane = threadIdx.x & 31, sub = lane % LANES, which = lane / LANES;
   const int heads = nh + 2 * nkv, qk = nh + nkv;
@@ -401,7 +401,8 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
                                             T* __restrict__ vcache, int flags, int heads_per_cta) {
   extern __shared__ float trig[];   // cos [rot / 2], sin [rot / 2]
   pdl_release_next();
-  pdl_wait_prior();
+  // positions, slots and the page table are the step's inputs: the angles and the page are worked
+  // out while the kernel before this one (which makes q, k and v) is still running
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   const int half = (flags & FLAG_ROPE) ? rot / 2 : 0;
@@ -412,6 +413,7 @@ __global__ void head_norm_rope_cache_kernel(T* __restrict__ qkv, int ntok, int n
     page = kv.page_table[(size_t)seq_slot[tok_seq[t]] * kv.table_width + (pos / kv.page_size) % kv.table_width];
   for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
   __syncthreads();
+  pdl_wait_prior();
   const int heads = nh + 2 * nkv, h0 = blockIdx.y * heads_per_cta;
   const int h1 = min(heads, h0 + heads_per_cta);
   for (int h = h0 + (threadIdx.x >> 5); h < h1; h += blockDim.x >> 5)
