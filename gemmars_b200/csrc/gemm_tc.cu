@@ -35,7 +35,26 @@ constexpr int THREADS = 192;
 // EPI_SWIGLU_BF16: W stacks a gate matrix over an up matrix ([2N, K]); the CTA keeps two
 // accumulators (gate rows and up rows of the same 128 features against one tile of x) and
 // writes silu(gate) * up in bfloat16, so the [M, 2N] intermediate never exists.
-enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2, EPI_SWIGLU_BF16 = 3 };
+enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_QKV_BF16 = 4 };
+
+// EPI_QKV_BF16: the q/k/v product of a decode step whose head size is the tile's 128 features: a
+// tile is one head of one kind, and the epilogue does what the per-head kernel would do next on
+// the value it holds in a register: RMSNorm over the head, rotation at the token's position, the
+// query's scale; queries go to y as bfloat16, keys and values straight into the paged cache
+// (src/qwen.rs:737-785).  What that needs beyond the product:
+struct QkvTail {
+  const float* q_weight;    // [128] or null: no norm
+  const float* k_weight;
+  const float* inv_freq;    // [64] or null: no rotation
+  const int* tok_pos;
+  const int* tok_seq;
+  const int* seq_slot;
+  const int* page_table;    // null: keys and values are not cached (they go to y like the queries)
+  bf16* kcache;
+  bf16* vcache;
+  float eps, q_scale;
+  int nh, nkv, table_width, page_size;
+};
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
 
 __device__ int g_status;   // first failure of any launch; 0 when all waits completed
@@ -66,6 +85,46 @@ __device__ __forceinline__ void emit(void* y, size_t idx, float v) {
   else ((float*)y)[idx] += v;
 }
 
+// One value of one token of one head tile, held by epilogue thread f = feature; all 128 epilogue
+// threads call it together.  red: 4 floats, xs: 128 floats of shared memory.
+__device__ __forceinline__ void qkv_finish(const QkvTail& tl, void* y, long long ldy, int m, int n0, int f, float value,
+                                           float* red, float* xs) {
+  const int head = n0 / BM;
+  const int pos = tl.tok_pos[m];
+  const bool is_q = head < tl.nh, is_k = !is_q && head < tl.nh + tl.nkv;
+  size_t cache_row = 0;   // (page * kv heads + kv head): the page's rows of this kv head
+  if (!is_q && tl.page_table) {
+    const int slot = tl.seq_slot[tl.tok_seq[m]];
+    const int page = tl.page_table[(size_t)slot * tl.table_width + (pos / tl.page_size) % tl.table_width];
+    cache_row = (size_t)page * tl.nkv + (head - tl.nh - (is_k ? 0 : tl.nkv));
+  }
+  if (!is_q && !is_k) {   // a value head: as it is, into the transposed page
+    if (tl.page_table) tl.vcache[(cache_row * BM + f) * tl.page_size + pos % tl.page_size] = __float2bfloat16_rn(value);
+    else ((bf16*)y)[(size_t)m * ldy + n0 + f] = __float2bfloat16_rn(value);
+    return;
+  }
+  const float* w = is_q ? tl.q_weight : tl.k_weight;
+  float c = 1.f, sn = 0.f;
+  if (tl.inv_freq) sincosf((float)pos * tl.inv_freq[f & 63], &sn, &c);
+  float x = value;
+  if (w) {
+    const float part = warp_sum(value * value);
+    if ((f & 31) == 0) red[f >> 5] = part;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    x = value * (1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)BM + tl.eps)) * w[f];
+  }
+  xs[f] = x;
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  const float other = xs[f ^ 64];
+  asm volatile("bar.sync 1, 128;" ::: "memory");   // red and xs may be written again
+  // rotate-half: dims i and i + 64 are a pair (a, b): a' = a cos - b sin, b' = b cos + a sin
+  float r = f < 64 ? x * c - other * sn : x * c + other * sn;
+  if (is_q) r *= tl.q_scale;
+  const bf16 o = __float2bfloat16_rn(r);
+  if (is_q || !tl.page_table) ((bf16*)y)[(size_t)m * ldy + n0 + f] = o;
+  else tl.kcache[(cache_row * tl.page_size + pos % tl.page_size) * BM + f] = o;
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -75,8 +134,10 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy) {
+               const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy,
+               const __grid_constant__ QkvTail tail) {
   constexpr bool DUAL = MODE == EPI_SWIGLU_BF16;
+  __shared__ float qkv_red[MODE == EPI_QKV_BF16 ? 4 : 1], qkv_xs[MODE == EPI_QKV_BF16 ? BM : 1];
   constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = (DUAL ? 2 : 1) * W_BYTES, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN, TMEM_COLS = ACC_COLS < 32 ? 32 : ACC_COLS;
@@ -239,6 +300,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
           const int c = base + i;
+          if (MODE == EPI_QKV_BF16) {
+            if (c >= c1) continue;   // the same for every thread: they finish a token together
+            float head_v = v[i][0];
+#pragma unroll
+            for (int r = 1; r < 8; ++r) head_v += v[i][r];
+            qkv_finish(tail, y, ldy, m0 + c, n0, f, head_v + bias_v, qkv_red, qkv_xs);
+            continue;
+          }
           if (c >= c1 || n >= N) continue;
           float acc = v[i][0];
 #pragma unroll
@@ -279,7 +348,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       } else {
         tc_wait_ld();
       }
-      if (n < N) {
+      if (MODE == EPI_QKV_BF16) {
+        for (int j = 0; j < 16; ++j)   // the token count is the same for every thread
+          if (m0 + c + j < M) qkv_finish(tail, y, ldy, m0 + c + j, n0, f, __uint_as_float(v[j]) + b, qkv_red, qkv_xs);
+      } else if (n < N) {
         if (MODE == EPI_ACCUMULATE_F32) {
           // all 16 loads first, then the stores: a load after a store to the same array would
           // wait for it, and the chunk would take 16 round trips to memory instead of one
@@ -518,7 +590,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
 template <int BN, int STAGES, int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K, long long ldy,
-           int splits, cudaStream_t stream) {
+           int splits, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
   constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
   constexpr size_t STAGE = (size_t)NW * BM * BK * 2 + BN * BK * 2;
   constexpr size_t SMEM = (size_t)STAGES * STAGE + (2 * STAGES + 1) * 8 + 16 + 1024;
@@ -545,7 +617,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = GB_PDL ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, bias, y, M, N, K, ldy);
+  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, bias, y, M, N, K, ldy, tail);
 }
 
 template <int BN, int STAGES>
@@ -622,6 +694,34 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
       return stages == 3 ? launch_mode<128, 3>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
                          : launch_mode<128, 6>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
     case 256: return launch_mode<256, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+  }
+  return GB_ERR_SIZE;
+}
+
+// The q/k/v product of a decode step with the per-head work in its epilogue (head size 128, at most
+// 64 tokens): y[M, N] gets the queries (normed, rotated, scaled; N = (nh + 2 nkv) * 128, rows ldy
+// apart; the key and value columns of y are written only when page_table is null), the cache the
+// keys and values.  q_weight / k_weight null: no norm; inv_freq null: no rotation.
+GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, const float* bias, void* y, int M, int N, int K, long long ldx,
+                             long long ldy, int bn, int splits, const float* q_weight, const float* k_weight,
+                             const float* inv_freq, float eps, float q_scale, int nh, int nkv, const int* tok_pos,
+                             const int* tok_seq, const int* seq_slot, const int* page_table, int table_width,
+                             int page_size, void* kcache, void* vcache, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return GB_ERR_SIZE;
+  if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return GB_ERR_ARG;
+  if (M > 64 || nh <= 0 || nkv < 0 || N != (nh + 2 * nkv) * BM || !tok_pos) return GB_ERR_SIZE;
+  if (page_table && (!tok_seq || !seq_slot || !kcache || !vcache || page_size <= 0)) return GB_ERR_ARG;
+  if ((q_weight == nullptr) != (k_weight == nullptr)) return GB_ERR_ARG;
+  CUtensorMap mw, mx;
+  if (!tensor_map(&mw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
+  if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  QkvTail tail{q_weight, k_weight, inv_freq, tok_pos, tok_seq, seq_slot, page_table, (bf16*)kcache, (bf16*)vcache,
+               eps, q_scale, nh, nkv, table_width, page_size};
+  switch (bn) {
+    case 16: return launch<16, 4, EPI_QKV_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream, tail);
+    case 32: return launch<32, 4, EPI_QKV_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream, tail);
+    case 64: return launch<64, 4, EPI_QKV_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream, tail);
   }
   return GB_ERR_SIZE;
 }

@@ -300,6 +300,47 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
              ctas, _stream()), "gemm_tc_persistent")
 
 
+# measured on the 8B shape: +1.5 % tokens/s at batch 1 and 8, -1 % at batch 64 (a rank then finishes
+# eight tokens one after the other, three barriers each)
+QKV_FUSED_MAX_TOKENS = 32
+
+
+def gemm_qkv_usable(x, w, nh: int, nkv: int, hd: int, rot: int) -> bool:
+    """Whether the q/k/v product of a step can do the per-head work in its epilogue: a decode step
+    in bfloat16 with heads of 128 (a head is a tile of the product), rotated over all dims or not
+    at all."""
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= QKV_FUSED_MAX_TOKENS and hd == 128 and rot in (0, hd)
+            and w.shape[0] == (nh + 2 * nkv) * hd and gemm_tc_usable(x, w))
+
+
+def gemm_qkv(x, w, bias, qkv, nh, nkv, hd, q_weight, k_weight, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot,
+             page_table, page_size, kcache, vcache, bn=None, splits=None):
+    """qkv[:, :nh*hd] = the step's queries, normed per head, rotated and scaled; the keys (normed,
+    rotated) and the values go into the paged cache (``page_table`` None: into qkv as well): the
+    q/k/v product and head_norm_rope_cache in one kernel.  See gemm_qkv_usable."""
+    _cuda(x, w, bias, qkv, q_weight, k_weight, inv_freq, tok_pos, tok_seq, seq_slot, page_table, kcache, vcache)
+    m, k = x.shape
+    n = w.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.shape == (m, n) and qkv.stride(1) == 1 and w.is_contiguous()
+    if not gemm_qkv_usable(x, w, nh, nkv, hd, hd if inv_freq is not None else 0):
+        raise KernelError(f"gemm_qkv: needs bfloat16, at most {QKV_FUSED_MAX_TOKENS} tokens and heads of 128")
+    if page_table is not None:
+        assert kcache.dtype == torch.bfloat16 and kcache.is_contiguous() and kcache.shape[1:] == (nkv, page_size, hd)
+        assert vcache.is_contiguous() and vcache.shape[1:] == (nkv, hd, page_size)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+    auto_bn, auto_splits = gemm_tc_tiling(m, n, k)
+    f = _fn("gemm_tc", "gb_gemm_tc_qkv",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
+             c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), qkv.data_ptr(), m, n, k, x.stride(0), qkv.stride(0),
+             bn or auto_bn, splits or auto_splits, _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), eps, q_scale, nh, nkv,
+             tok_pos.data_ptr(), _ptr(tok_seq), _ptr(seq_slot), _ptr(page_table),
+             page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache), _ptr(vcache), _stream()),
+           "gemm_qkv")
+
+
 def gemm_swiglu(x, w_gate_up, out):
     """out[M, N] = silu(x @ gate.T) * (x @ up.T) for w_gate_up = [gate; up] of 2N rows: one
     tensor-core kernel in bfloat16; two kernels (product, then activation) otherwise."""

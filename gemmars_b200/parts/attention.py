@@ -90,6 +90,21 @@ class Attention(Part):
         nkv = self.num_kv_heads if self.has_kv else 0
         group, kc, vc = cache
         writes_cache = writes_cache and self.has_kv
+        rotary = self.position is None or isinstance(self.position, Rotary)
+        rot = self.position.rotary_dim if isinstance(self.position, Rotary) else 0
+        if rotary and ctx.max_new <= 1 and kernels.gemm_qkv_usable(h, self.qkv.weight, nh, nkv, hd, rot):
+            # a decode step with heads of 128: norm, rotation, scale and the cache write ride on the
+            # q/k/v product's epilogue
+            qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=h.dtype, device=h.device)
+            kernels.gemm_qkv(h, self.qkv.weight, self.qkv.bias, qkv, nh, nkv, hd,
+                             self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
+                             self.position.inv_freq(h.device) if rot else None, self.scale, ctx.tok_pos, ctx.tok_seq,
+                             ctx.seq_slot, group.page_table if writes_cache else None, group.page_size,
+                             kc if writes_cache else None, vc if writes_cache else None)
+            att = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
+            kernels.attention(ctx, qkv[:, :nh * hd], att, nh, kc, vc, group.page_table, group.page_size, self.window)
+            self.o.add_into(att, residual)
+            return
         qkv = self.qkv(h)
         norm = kernels.FLAG_NORM if self.qk_norm else 0
         store = kernels.FLAG_CACHE if writes_cache else 0

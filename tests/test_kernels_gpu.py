@@ -415,3 +415,55 @@ def test_dependent_launch_chain(k):
         build.set_pdl(False)
     assert (x - want).abs().max().item() <= 2e-2 * want.abs().max().item()
     assert k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("m,nh,nkv,kk,splits,bias,norm,rope", [(8, 4, 2, 512, None, False, True, True), (1, 2, 1, 256, 1, True, True, True),
+                                                                (31, 3, 3, 1024, 4, True, False, True), (32, 8, 0, 512, 8, False, True, False)])
+def test_gemm_qkv_against_product_then_head_kernel(k, m, nh, nkv, kk, splits, bias, norm, rope):
+    """The q/k/v product with norm, rotation, scale and cache write in its epilogue, against the
+    product in float32 followed by the same steps in PyTorch; the cache must get exactly the step's
+    rows and nothing else."""
+    torch.manual_seed(m + nh)
+    hd, n = 128, (nh + 2 * nkv) * 128
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(n, device="cuda") * 0.1 if bias else None
+    qw, kw = (torch.rand(hd, device="cuda") + 0.5, torch.rand(hd, device="cuda") + 0.5) if norm else (None, None)
+    inv = ((1.0 / torch.pow(torch.tensor(1e4, dtype=torch.float64), torch.arange(hd // 2, dtype=torch.float64) * 2 / hd))
+           .float().cuda() if rope else None)
+    eps, scale = 1e-5, hd ** -0.5
+    lengths = [70 + i for i in range(m)]                  # token i is position 69 + i of sequence i
+    kc, vc, table, _ = _paged(m, lengths, max(nkv, 1), hd, torch.bfloat16, seed=3)
+    kc.zero_(); vc.zero_()
+    tok_pos = torch.tensor([n_ - 1 for n_ in lengths], dtype=torch.int32, device="cuda")
+    tok_seq = torch.arange(m, dtype=torch.int32, device="cuda")
+    qkv = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    k.gemm_qkv(x, w, b, qkv, nh, nkv, hd, qw, kw, eps, inv, scale, tok_pos, tok_seq, tok_seq,
+               table if nkv else None, 64, kc if nkv else None, vc if nkv else None, splits=splits)
+    ref = (x.float() @ w.float().T + (b if bias else 0)).view(m, nh + 2 * nkv, hd)
+
+    def head(v, wt, pos, s):
+        if norm:
+            v = v * torch.rsqrt((v * v).mean() + eps) * wt
+        if rope:
+            ang = (torch.tensor(float(pos), device="cuda") * inv).double()
+            a, bb = v[:64].double(), v[64:].double()
+            v = torch.cat([a * torch.cos(ang) - bb * torch.sin(ang), bb * torch.cos(ang) + a * torch.sin(ang)]).float()
+        return v * s
+    got = qkv.float().view(m, nh + 2 * nkv, hd)
+    tol = 2 ** -7
+    for i in range(m):
+        pos = int(tok_pos[i])
+        page = int(table[i, pos // 64])
+        for h in range(nh):
+            want = head(ref[i, h], qw, pos, scale)
+            assert (got[i, h] - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+        for h in range(nkv):
+            want = head(ref[i, nh + h], kw, pos, 1.0)
+            assert (kc[page, h, pos % 64].float() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+            wantv = ref[i, nh + nkv + h]
+            assert (vc[page, h, :, pos % 64].float() - wantv).abs().max().item() <= tol * max(1.0, wantv.abs().max().item())
+    if nkv:
+        assert int((kc.abs().sum(dim=(1, 3)) > 0).sum()) == m    # one row per token and no other
+        assert float(kc[0].abs().sum()) == 0.0
+    assert k.gemm_tc_status() == 0
