@@ -87,3 +87,37 @@ def test_sharp_weights_make_faults_visible(sharp_model):
     pcfg, w = plain.load_folder(folder)
     changed = plain.forward(pcfg, w, toks[:200] + [(toks[200] + 1) % pcfg["vocab_size"]] + toks[201:])
     assert np.abs(changed[-1] - ref[-1]).max() > 1e-3 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+def test_prompts_cut_into_chunks_inside_one_step(sharp_model, mild_model, dtype, tol):
+    """One step whose prompts are longer than the chunk and than the step's token budget: the
+    runner feeds them in sub-steps of its own (some sequences wait for a later sub-step, the window
+    of the sliding layers is crossed inside a prompt), and the wanted rows come from different
+    sub-steps.  Against the plain implementation, and, in float32, bit for bit against a runner
+    that takes the prompts whole."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, toks, ref = sharp_model if dtype == "float32" else mild_model
+    scale = float(np.abs(ref).max())
+    model = build_model(folder, dtype=dtype)
+    prompts = [toks[:150], toks[:7], toks[:97]]
+    wants = [[0, 15, 16, 79, 149], [6], [31, 32, 96]]
+
+    def run(**kw):
+        runner = Runner(model, max_tokens=64 * 12, max_batch=4, **kw)
+        slots = [runner.open() for _ in prompts]
+        out = runner.step([StepItem(s, p, w) for s, p, w in zip(slots, prompts, wants)]).cpu().numpy()
+        # and the sequences go on afterwards from what the sub-steps left in the cache
+        nxt = runner.step([StepItem(slots[0], [toks[150]], [0]), StepItem(slots[2], [toks[97]], [0])]).cpu().numpy()
+        return out, nxt
+    cut, cut_next = run(prefill_chunk=16, max_step_tokens=40)
+    rows = [ref[w] for ws in wants for w in ws]
+    assert cut.shape == (len(rows), ref.shape[1])
+    for got, want in zip(cut, rows):
+        assert np.abs(got - want).max() <= tol * scale
+    assert np.abs(cut_next[0] - ref[150]).max() <= tol * scale and np.abs(cut_next[1] - ref[97]).max() <= tol * scale
+    whole, whole_next = run()
+    if dtype == "float32":
+        assert np.array_equal(cut, whole) and np.array_equal(cut_next, whole_next)
+    else:
+        assert np.abs(cut - whole).max() <= tol * scale
