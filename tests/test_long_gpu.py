@@ -121,3 +121,44 @@ def test_prompts_cut_into_chunks_inside_one_step(sharp_model, mild_model, dtype,
         assert np.array_equal(cut, whole) and np.array_equal(cut_next, whole_next)
     else:
         assert np.abs(cut - whole).max() <= tol * scale
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+def test_a_batch_of_seventy_sequences(mild_model, dtype, tol):
+    """More sequences than the decode kernels' 64-token tiles: the prompts in one step, then single
+    tokens for all of them (replayed from a graph padded to 128 rows), then for the half that goes
+    on after the others were closed and their slots given to new sequences."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, toks, _ = mild_model
+    pcfg, w = plain.load_folder(folder)
+    model = build_model(folder, dtype=dtype)
+    runner = Runner(model, max_tokens=64 * 160, max_batch=80)
+    rng = np.random.default_rng(11)
+    seqs = [rng.integers(0, pcfg["vocab_size"], int(rng.integers(6, 15))).tolist() for _ in range(70)]
+    slots = [runner.open() for _ in seqs]
+    fed = [len(s) - 4 for s in seqs]
+    got = {i: [] for i in range(70)}
+    first = runner.step([StepItem(sl, s[:n], [n - 1]) for sl, s, n in zip(slots, seqs, fed)]).cpu().numpy()
+    for i in range(70):
+        got[i].append(first[i])
+    for step in range(2):
+        out = runner.step([StepItem(sl, [s[n + step]], [0]) for sl, s, n in zip(slots, seqs, fed)]).cpu().numpy()
+        for i in range(70):
+            got[i].append(out[i])
+    for i in range(35, 70):
+        runner.close(slots[i])
+    new = [rng.integers(0, pcfg["vocab_size"], 9).tolist() for _ in range(20)]
+    new_slots = [runner.open() for _ in new]
+    assert set(new_slots) & set(slots[35:])                       # slots are used again
+    new_out = runner.step([StepItem(sl, s, [8]) for sl, s in zip(new_slots, new)]).cpu().numpy()
+    out = runner.step([StepItem(slots[i], [seqs[i][fed[i] + 2]], [0]) for i in range(35)]).cpu().numpy()
+    for i in range(35):
+        got[i].append(out[i])
+    for i in list(range(0, 70, 9)) + [34, 69]:
+        ref = plain.forward(pcfg, w, seqs[i])
+        scale = float(np.abs(ref).max())
+        for k_, row in enumerate(got[i]):
+            assert np.abs(row - ref[fed[i] - 1 + k_]).max() <= tol * scale, (i, k_)
+    for j in (0, 19):
+        ref = plain.forward(pcfg, w, new[j])
+        assert np.abs(new_out[j] - ref[8]).max() <= tol * float(np.abs(ref).max())
