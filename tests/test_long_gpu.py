@@ -162,3 +162,32 @@ def test_a_batch_of_seventy_sequences(mild_model, dtype, tol):
     for j in (0, 19):
         ref = plain.forward(pcfg, w, new[j])
         assert np.abs(new_out[j] - ref[8]).max() <= tol * float(np.abs(ref).max())
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+def test_heads_of_128_prompt_then_decoding(tmp_path_factory, dtype, tol):
+    """A narrow model with heads of 128, so that the engine itself (not only the kernel tests) runs
+    the kernels that the released sizes use: a 700-token prompt (tensor-core prompt attention over
+    several tiles, the wide rotation kernel, the row-per-warp norm), a second prompt beside it, then
+    forty single tokens for both (streaming decode attention over a dozen pages with a window on
+    one layer, the q/k/v product with the per-head work in its epilogue, graphs)."""
+    from tiny_configs import SMALL_128
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    from gemmars_b200.weights import write_random_model
+    folder = str(tmp_path_factory.mktemp("small128"))
+    write_random_model(folder, SMALL_128, seed=4)
+    pcfg, w = plain.load_folder(folder)
+    rng = np.random.default_rng(8)
+    a, b = rng.integers(0, 1003, 740).tolist(), rng.integers(0, 1003, 130).tolist()
+    ra, rb = plain.forward(pcfg, w, a), plain.forward(pcfg, w, b)
+    scale = float(max(np.abs(ra).max(), np.abs(rb).max()))
+    model = build_model(folder, dtype=dtype)
+    runner = Runner(model, max_tokens=64 * 20, max_batch=2)
+    sa, sb = runner.open(), runner.open()
+    out = runner.step([StepItem(sa, a[:700], [0, 127, 128, 699]), StepItem(sb, b[:90], [89])]).cpu().numpy()
+    for got, want in zip(out, [ra[0], ra[127], ra[128], ra[699], rb[89]]):
+        assert np.abs(got - want).max() <= tol * scale
+    for i in range(40):
+        out = runner.step([StepItem(sa, [a[700 + i]], [0]), StepItem(sb, [b[90 + i]], [0])]).cpu().numpy()
+        assert np.abs(out[0] - ra[700 + i]).max() <= tol * scale, i
+        assert np.abs(out[1] - rb[90 + i]).max() <= tol * scale, i

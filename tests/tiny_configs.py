@@ -28,3 +28,16 @@ TINY_C = {
     "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": False,
     "partial_rotary_factor": 0.5, "max_position_embeddings": 1024,
 }
+
+# Heads of 128 as the released models have (few of them, a narrow model): the shapes at which the
+# tensor-core attention kernels, the streaming decode attention and the fused q/k/v product apply.
+# A window on one layer, biases, a vocabulary that is no multiple of anything.
+SMALL_128 = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 384, "vocab_size": 1003, "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
+    "max_position_embeddings": 2048, "eos_token_id": 5,
+    "use_sliding_window": True, "sliding_window": 200,
+    "layer_types": ["full_attention", "sliding_attention"],
+}
