@@ -191,3 +191,33 @@ def test_heads_of_128_prompt_then_decoding(tmp_path_factory, dtype, tol):
         out = runner.step([StepItem(sa, [a[700 + i]], [0]), StepItem(sb, [b[90 + i]], [0])]).cpu().numpy()
         assert np.abs(out[0] - ra[700 + i]).max() <= tol * scale, i
         assert np.abs(out[1] - rb[90 + i]).max() <= tol * scale, i
+
+
+def test_released_width_bfloat16_against_float32():
+    """The layer sizes of a released model (hidden 4096, 32 / 8 heads of 128, intermediate 12288,
+    vocabulary 151936; two layers, random weights): the bfloat16 engine, whose products, splits and
+    tiles are the ones that serving uses at this width, against the float32 engine on the same
+    weights, for two unequal prompts and a dozen single tokens.  (The float32 engine is checked
+    against the plain implementation at small sizes; the plain implementation is too slow here.)"""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    from gemmars_b200.weights import random_weights
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 4096,
+           "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+           "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False,
+           "tie_word_embeddings": False, "max_position_embeddings": 4096}
+    tensors = random_weights(cfg, seed=0, device="cuda:0")
+    rng = np.random.default_rng(0)
+    a, b = rng.integers(0, cfg["vocab_size"], 330).tolist(), rng.integers(0, cfg["vocab_size"], 75).tolist()
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        model = build_model(raw_config=cfg, tensors=tensors, dtype=dtype, device="cuda:0")
+        runner = Runner(model, max_tokens=64 * 16, max_batch=2)
+        sa, sb = runner.open(), runner.open()
+        rows = [runner.step([StepItem(sa, a[:300], [0, 150, 299]), StepItem(sb, b[:60], [59])]).float().cpu().numpy()]
+        for i in range(12):
+            rows.append(runner.step([StepItem(sa, [a[300 + i]], [0]), StepItem(sb, [b[60 + i]], [0])]).float().cpu().numpy())
+        res[dtype] = np.concatenate(rows)
+        del runner, model
+    ref, got = res["float32"], res["bfloat16"]
+    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
+    # (with random weights the largest of 151,936 logits leads by less than that: no check of the argmax)
