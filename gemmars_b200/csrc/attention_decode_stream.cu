@@ -1,5 +1,6 @@
 // bfloat16 attention of single positions over the paged cache, with the cache streamed through
-// shared memory by TMA (sm_100a; head sizes 64, 128, 192, 256; at most 16 query heads per kv head):
+// shared memory by TMA (sm_100a; head sizes that are multiples of 64, of which the package uses and tests 64 and 128;
+// at most 16 query heads per kv head):
 //
 //     s_j = q_h . K[j, g]   for lo <= j <= p,      p_j = softmax(s)_j,      o_h = sum_j p_j V[j, g]
 //     (src/model.rs:1199-1226; src/kernels.rs:1550-1561; q arrives scaled by head_dim^-0.5)
