@@ -76,13 +76,109 @@ __device__ __forceinline__ void trace(int slot) {
 #endif
 
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+// silu(g) * u with the hardware's exp2 and reciprocal (two special-function instructions): the
+// result is rounded to bfloat16, whose step is a thousand times their error, and the four epilogue
+// warps have nothing to hide a longer chain behind (measured: the exact expf and division made
+// the gated tile's epilogue 11.5 us per 128 tokens).  For g below -88 the quotient is 0, the limit.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
 
 template <int MODE>
 __device__ __forceinline__ void emit(void* y, size_t idx, float v) {
   if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16) ((bf16*)y)[idx] = __float2bfloat16_rn(v);
   else if (MODE == EPI_STORE_F32) ((float*)y)[idx] = v;
   else ((float*)y)[idx] += v;
+}
+
+// The way out of a tile for results that TMA can address.  An epilogue warp holds 32 features (one
+// per lane) of 16 tokens at a time; written to the result with plain stores that is 16 requests of
+// 64 or 128 bytes per warp, and the requests, not their bytes, were what the epilogue waited for
+// (measured: 0.55 us per 16 tokens whatever the type, 4.6 us for a tile of 128 tokens; a quarter of
+// the stores took a third of the time).  Here the warp puts the piece into shared memory, token
+// after token, and one lane sends it as a single TMA store (or float32 add: the residual), two
+// pieces in flight per warp.  TMA drops the tokens and features beyond the result's edges.  A
+// piece's cost is its fence and its request (about 400 cycles, whatever its size), so a piece is
+// 32 tokens wherever the tile has that many.
+constexpr int PIECE_TOKENS = TC_OUT_ROWS, PIECE_FEATURES = TC_OUT_COLS;
+constexpr int PIECE_BYTES = PIECE_TOKENS * PIECE_FEATURES * 4;          // float32; bfloat16 uses half
+constexpr int PIECES = 2;                                               // pieces of a warp in flight
+constexpr int OUT_STAGING_BYTES = 4 * PIECES * PIECE_BYTES;             // four warps
+
+template <int MODE>
+struct TileOut {
+  const CUtensorMap* map;
+  uint8_t* pieces;   // this warp's pieces, 128-byte aligned
+  uint32_t sent;
+  __device__ __forceinline__ TileOut(const CUtensorMap* m, uint8_t* staging, int warp)
+      : map(m), pieces(staging + warp * PIECES * PIECE_BYTES), sent(0) {}
+  __device__ __forceinline__ static void put(uint8_t* p, int token, int lane, float r) {
+    if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16) ((bf16*)p)[token * PIECE_FEATURES + lane] = __float2bfloat16_rn(r);
+    else ((float*)p)[token * PIECE_FEATURES + lane] = r;
+  }
+  // lo, hi: tokens 0-15 and (with `both`) 16-31 of this lane's feature; x: the warp's first
+  // feature; row: the first token.  The map's pieces are 32 tokens long with `both`, else 16.
+  __device__ __forceinline__ void send(const uint32_t (&lo)[16], const uint32_t (&hi)[16], bool both, float bias, int lane,
+                                       int x, int row, int N) {
+    uint8_t* p = pieces + (sent % PIECES) * PIECE_BYTES;
+    if (sent >= PIECES) {   // the piece sent PIECES calls ago has left this memory
+      if (lane == 0) tma_store_wait_read<PIECES - 1>();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) put(p, j, lane, __uint_as_float(lo[j]) + bias);
+    if (both) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) put(p, 16 + j, lane, __uint_as_float(hi[j]) + bias);
+    }
+    fence_smem_to_tma();
+    __syncwarp();
+    if (lane == 0 && x < N) {
+      if (MODE == EPI_ACCUMULATE_F32) tma_add_2d(map, p, x, row);
+      else tma_store_2d(map, p, x, row);
+      tma_store_commit();
+    }
+    ++sent;
+  }
+  // before the shared memory is given up and the kernel ends
+  __device__ __forceinline__ void finish(int lane) {
+    if (lane == 0) tma_store_wait_all();
+    __syncwarp();
+  }
+};
+
+// 16 tokens (from m_first) of feature n with plain stores: results that TMA cannot address.
+template <int MODE>
+__device__ __forceinline__ void store_direct(void* y, long long ldy, const uint32_t (&v)[16], float bias, int m_first, int M,
+                                             int n, int N) {
+  if (n >= N) return;
+  if (MODE == EPI_ACCUMULATE_F32) {
+    // all 16 loads first, then the stores: a load after a store to the same array would
+    // wait for it, and the chunk would take 16 round trips to memory instead of one
+    float old[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) old[j] = m_first + j < M ? ((const float*)y)[(size_t)(m_first + j) * ldy + n] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (m_first + j < M) ((float*)y)[(size_t)(m_first + j) * ldy + n] = old[j] + __uint_as_float(v[j]) + bias;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+      if (m_first + j < M) emit<MODE>(y, (size_t)(m_first + j) * ldy + n, __uint_as_float(v[j]) + bias);
+  }
+}
+
+// The accumulator columns [c, c + 16) of this warp's 32 lanes, gated when the tile has two
+// accumulators BN columns apart; the caller waits (tc_wait_ld) before it reads v, then calls gate.
+template <bool DUAL>
+__device__ __forceinline__ void acc_load(uint32_t acc, int up_offset, int c, uint32_t (&v)[16], uint32_t (&u)[16]) {
+  tc_ld16(acc + c, v);
+  if (DUAL) tc_ld16(acc + up_offset + c, u);
+}
+template <bool DUAL>
+__device__ __forceinline__ void gate(uint32_t (&v)[16], const uint32_t (&u)[16]) {
+  if (DUAL) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+  }
 }
 
 // One value of one token of one head tile, held by epilogue thread f = feature; all 128 epilogue
@@ -134,8 +230,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-               const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy,
-               const __grid_constant__ QkvTail tail) {
+               const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
+               void* __restrict__ y, int M, int N, int K, long long ldy, const __grid_constant__ QkvTail tail) {
   constexpr bool DUAL = MODE == EPI_SWIGLU_BF16;
   __shared__ float qkv_red[MODE == EPI_QKV_BF16 ? 4 : 1], qkv_xs[MODE == EPI_QKV_BF16 ? BM : 1];
   constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = (DUAL ? 2 : 1) * W_BYTES, B_BYTES = BN * BK * 2;
@@ -334,47 +430,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else if (warp < 4 && have_acc) {
     const int f = warp * 32 + lane, n = n0 + f;
     const float b = bias_v;
+    // the pipeline's stages are idle by now: the pieces on their way out lie there
+    TileOut<MODE> tile_out(&map_y, smem, warp);
+    const bool by_tma = MODE != EPI_QKV_BF16 && y_tma != 0;
+    constexpr bool BOTH = BN >= 32;   // 32 tokens per round
+    const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 16) {
+    for (int c = 0; c < BN; c += BOTH ? 32 : 16) {
       if (m0 + c >= M) break;
-      uint32_t v[16];
-      tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
-      if (DUAL) {
-        uint32_t u[16];
-        tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + BN + c, u);
-        tc_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
-      } else {
-        tc_wait_ld();
-      }
-      if (MODE == EPI_QKV_BF16) {
+      uint32_t v[16], u[16], v2[16], u2[16];
+      acc_load<DUAL>(acc, BN, c, v, u);
+      if (BOTH) acc_load<DUAL>(acc, BN, c + 16, v2, u2);
+      tc_wait_ld();
+      gate<DUAL>(v, u);
+      if (BOTH) gate<DUAL>(v2, u2);
+      if (by_tma) {
+        tile_out.send(v, v2, BOTH, b, lane, n0 + warp * 32, m0 + c, N);
+      } else if (MODE == EPI_QKV_BF16) {
         for (int j = 0; j < 16; ++j)   // the token count is the same for every thread
           if (m0 + c + j < M) qkv_finish(tail, y, ldy, m0 + c + j, n0, f, __uint_as_float(v[j]) + b, qkv_red, qkv_xs);
-      } else if (n < N) {
-        if (MODE == EPI_ACCUMULATE_F32) {
-          // all 16 loads first, then the stores: a load after a store to the same array would
-          // wait for it, and the chunk would take 16 round trips to memory instead of one
-          float old[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c + j;
-            old[j] = m < M ? ((const float*)y)[(size_t)m * ldy + n] : 0.f;
-          }
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c + j;
-            if (m < M) ((float*)y)[(size_t)m * ldy + n] = old[j] + __uint_as_float(v[j]) + b;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c + j;
-            if (m < M) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + b);
-          }
-        }
+        if (BOTH)
+          for (int j = 0; j < 16; ++j)
+            if (m0 + c + 16 + j < M) qkv_finish(tail, y, ldy, m0 + c + 16 + j, n0, f, __uint_as_float(v2[j]) + b, qkv_red, qkv_xs);
+      } else {
+        store_direct<MODE>(y, ldy, v, b, m0 + c, M, n, N);
+        if (BOTH) store_direct<MODE>(y, ldy, v2, b, m0 + c + 16, M, n, N);
       }
     }
+    if (by_tma) tile_out.finish(lane);
   }
   if (threadIdx.x == 0) TRACE(6);
   tc_fence_before();
@@ -414,7 +497,8 @@ __device__ long long g_ptrace[256 * 8];
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                          const float* __restrict__ bias, void* __restrict__ y, int M, int N, int K, long long ldy, int bn) {
+                          const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
+                          void* __restrict__ y, int M, int N, int K, long long ldy, int bn) {
   constexpr bool DUAL = MODE == EPI_SWIGLU_BF16;
   constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = (DUAL ? 2 : 1) * W_BYTES, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -430,6 +514,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   uint64_t* acc_full = empty_bar + STAGES;     // 2: the MMA warp has finished a tile in that buffer
   uint64_t* acc_empty = acc_full + 2;          // 2: the epilogue warps have read it out
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+  uint8_t* out_staging = smem + STAGES * STAGE_BYTES + 1024;   // past the barriers; OUT_STAGING_BYTES
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_m = (M + bn - 1) / bn, tiles_n = (N + BM - 1) / BM, tiles = tiles_m * tiles_n;
@@ -524,6 +609,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     // ---------------- epilogue warps: lane = feature, column = token
     pdl_wait_prior();
     const int f = warp * 32 + lane;
+    TileOut<MODE> tile_out(&map_y, out_staging, warp);
+    const bool both = bn % 32 == 0;   // 32 tokens per round; the result's map is cut to match
     uint32_t i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
       const uint32_t b = i & 1;
@@ -539,39 +626,19 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       const float bv = (bias && n < N) ? bias[n] : 0.f;
       const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16) + b * ACC_COLS;
 #pragma unroll 1
-      for (int c = 0; c < bn; c += 16) {
+      for (int c = 0; c < bn; c += both ? 32 : 16) {
         if (m0 + c >= M) break;
-        uint32_t v[16];
-        tc_ld16(acc + c, v);
-        if (DUAL) {
-          uint32_t u[16];
-          tc_ld16(acc + BN + c, u);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
+        uint32_t v[16], u[16], v2[16], u2[16];
+        acc_load<DUAL>(acc, BN, c, v, u);
+        if (both) acc_load<DUAL>(acc, BN, c + 16, v2, u2);
+        tc_wait_ld();
+        gate<DUAL>(v, u);
+        if (both) gate<DUAL>(v2, u2);
+        if (y_tma) {
+          tile_out.send(v, v2, both, bv, lane, n0 + warp * 32, m0 + c, N);
         } else {
-          tc_wait_ld();
-        }
-        if (n < N) {
-          if (MODE == EPI_ACCUMULATE_F32) {
-            float old[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c + j;
-              old[j] = m < M ? ((const float*)y)[(size_t)m * ldy + n] : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c + j;
-              if (m < M) ((float*)y)[(size_t)m * ldy + n] = old[j] + __uint_as_float(v[j]) + bv;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = m0 + c + j;
-              if (m < M) emit<MODE>(y, (size_t)m * ldy + n, __uint_as_float(v[j]) + bv);
-            }
-          }
+          store_direct<MODE>(y, ldy, v, bv, m0 + c, M, n, N);
+          if (both) store_direct<MODE>(y, ldy, v2, bv, m0 + c + 16, M, n, N);
         }
       }
       tc_fence_before();
@@ -579,6 +646,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       if (lane == 0) mbar_arrive(&acc_empty[b]);
       if (threadIdx.x == 0) PTRACE(i, 4);   // epilogue: tile i stored
     }
+    if (y_tma) tile_out.finish(lane);
   }
   tc_fence_before();
   __syncthreads();
@@ -588,14 +656,29 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
 // ------------------------------------------------------------------ host side
 
+// The result's tensor map, and whether TMA can address the result at all.
+struct OutMap {
+  CUtensorMap map;
+  int usable;
+};
+// bn: tokens per tile; the kernels send 32 tokens at a time where a tile has that many.
+OutMap out_map(const void* y, int mode, int M, int N, long long ldy, int bn) {
+  OutMap o = {};
+  const bool f32 = mode == EPI_STORE_F32 || mode == EPI_ACCUMULATE_F32;
+  o.usable = mode != EPI_QKV_BF16 && tensor_map_out(&o.map, y, (uint64_t)M, (uint64_t)N, (uint64_t)ldy * (f32 ? 4 : 2),
+                                                    bn % 32 == 0 ? 32 : 16, f32);
+  return o;
+}
+
 template <int BN, int STAGES, int MODE>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K, long long ldy,
-           int splits, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M, int N, int K,
+           long long ldy, int splits, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
   constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
   constexpr size_t STAGE = (size_t)NW * BM * BK * 2 + BN * BK * 2;
   constexpr size_t SMEM = (size_t)STAGES * STAGE + (2 * STAGES + 1) * 8 + 16 + 1024;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
   static_assert(BN > 64 || (size_t)NW * BN * BM * 4 <= (size_t)STAGES * STAGE, "partial sums need the stage memory");
+  static_assert((size_t)OUT_STAGING_BYTES <= (size_t)STAGES * STAGE, "the pieces on their way out need the stage memory");
   auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
   static bool configured = false;
   if (!configured) {
@@ -617,25 +700,27 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = GB_PDL ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, bias, y, M, N, K, ldy, tail);
+  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, tail);
 }
 
 template <int BN, int STAGES>
-int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K,
-                long long ldy, int splits, cudaStream_t stream) {
+int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
+                int N, int K, long long ldy, int splits, cudaStream_t stream) {
   switch (mode) {
-    case EPI_STORE_BF16: return launch<BN, STAGES, EPI_STORE_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
-    case EPI_STORE_F32: return launch<BN, STAGES, EPI_STORE_F32>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
-    case EPI_ACCUMULATE_F32: return launch<BN, STAGES, EPI_ACCUMULATE_F32>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+    case EPI_STORE_BF16: return launch<BN, STAGES, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+    case EPI_STORE_F32: return launch<BN, STAGES, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+    case EPI_ACCUMULATE_F32: return launch<BN, STAGES, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
   }
   return GB_ERR_ARG;
 }
 
 template <int BN, int STAGES, int MODE>
-int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const float* bias, void* y, int M, int N, int K,
-                      long long ldy, int bn, int ctas, cudaStream_t stream) {
+int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
+                      int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream) {
   constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
-  constexpr size_t SMEM = (size_t)STAGES * ((size_t)NW * BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 4) * 8 + 16 + 1024;
+  // stages, 1 KB of barriers, the pieces on their way out, 1 KB to align the base
+  constexpr size_t SMEM = (size_t)STAGES * ((size_t)NW * BM * BK * 2 + BN * BK * 2) + 1024 + OUT_STAGING_BYTES + 1024;
+  static_assert((2 * STAGES + 4) * 8 + 16 <= 1024, "the barriers have 1 KB");
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
   auto kernel = gemm_tc_persistent_kernel<BN, STAGES, MODE>;
   static bool configured = false;
@@ -645,7 +730,8 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const float*
     configured = true;
   }
   const int tiles = ((M + bn - 1) / bn) * ((N + BM - 1) / BM);
-  gb_launch(kernel, dim3(tiles < ctas ? tiles : ctas), dim3(THREADS), SMEM, stream, mw, mx, bias, y, M, N, K, ldy, bn);
+  gb_launch(kernel, dim3(tiles < ctas ? tiles : ctas), dim3(THREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N,
+            K, ldy, bn);
   return gb_launch_status();
 }
 
@@ -668,13 +754,14 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
   if (swiglu && bias) return GB_ERR_ARG;
   if (!tensor_map(&mw, w, (uint64_t)N * (swiglu ? 2 : 1), (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  const OutMap my = out_map(y, mode, M, N, ldy, bn);
   if (swiglu) {
     switch (bn) {
-      case 16: return launch<16, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
-      case 32: return launch<32, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
-      case 64: return launch<64, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
-      case 128: return launch<128, 4, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
-      case 256: return launch<256, 3, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      case 16: return launch<16, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      case 32: return launch<32, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      case 64: return launch<64, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      case 128: return launch<128, 4, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      case 256: return launch<256, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
     }
     return GB_ERR_SIZE;
   }
@@ -682,18 +769,18 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
     // decoding: `stages` = 4 leaves room for three CTAs on an SM (their tiles then finish together),
     // 8 gives one CTA a deeper pipeline
     case 16:
-      return stages == 8 ? launch_mode<16, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<16, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 8 ? launch_mode<16, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
+                         : launch_mode<16, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
     case 32:
-      return stages == 8 ? launch_mode<32, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<32, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 8 ? launch_mode<32, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
+                         : launch_mode<32, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
     case 64:
-      return stages == 8 ? launch_mode<64, 8>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<64, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 8 ? launch_mode<64, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
+                         : launch_mode<64, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
     case 128:   // stages = 3: two CTAs fit an SM, and one's epilogue runs under the other's MMAs
-      return stages == 3 ? launch_mode<128, 3>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<128, 6>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
-    case 256: return launch_mode<256, 4>(mode, mw, mx, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 3 ? launch_mode<128, 3>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
+                         : launch_mode<128, 6>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+    case 256: return launch_mode<256, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
   }
   return GB_ERR_SIZE;
 }
@@ -716,12 +803,13 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, const float* bias, vo
   CUtensorMap mw, mx;
   if (!tensor_map(&mw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  const OutMap my = out_map(y, EPI_QKV_BF16, M, N, ldy, bn);   // not used: the tail writes to the cache
   QkvTail tail{q_weight, k_weight, inv_freq, tok_pos, tok_seq, seq_slot, page_table, (bf16*)kcache, (bf16*)vcache,
                eps, q_scale, nh, nkv, table_width, page_size};
   switch (bn) {
-    case 16: return launch<16, 4, EPI_QKV_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream, tail);
-    case 32: return launch<32, 4, EPI_QKV_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream, tail);
-    case 64: return launch<64, 4, EPI_QKV_BF16>(mw, mx, bias, y, M, N, K, ldy, splits, stream, tail);
+    case 16: return launch<16, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+    case 32: return launch<32, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+    case 64: return launch<64, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
   }
   return GB_ERR_SIZE;
 }
@@ -739,21 +827,22 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
   CUtensorMap mw, mx;
   if (!tensor_map(&mw, w, (uint64_t)N * (swiglu ? 2 : 1), (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  const OutMap my = out_map(y, mode, M, N, ldy, bn);
   if (swiglu) {
     if (bn > 128) return GB_ERR_SIZE;
-    return launch_persistent<128, 4, EPI_SWIGLU_BF16>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
+    return launch_persistent<128, 4, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
   }
   if (bn > 128) {
     switch (mode) {
-      case EPI_STORE_BF16: return launch_persistent<256, 4, EPI_STORE_BF16>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
-      case EPI_STORE_F32: return launch_persistent<256, 4, EPI_STORE_F32>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
-      case EPI_ACCUMULATE_F32: return launch_persistent<256, 4, EPI_ACCUMULATE_F32>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_STORE_BF16: return launch_persistent<256, 4, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_STORE_F32: return launch_persistent<256, 4, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_ACCUMULATE_F32: return launch_persistent<256, 4, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
     }
   } else {
     switch (mode) {
-      case EPI_STORE_BF16: return launch_persistent<128, 6, EPI_STORE_BF16>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
-      case EPI_STORE_F32: return launch_persistent<128, 6, EPI_STORE_F32>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
-      case EPI_ACCUMULATE_F32: return launch_persistent<128, 6, EPI_ACCUMULATE_F32>(mw, mx, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_STORE_BF16: return launch_persistent<128, 6, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_STORE_F32: return launch_persistent<128, 6, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_ACCUMULATE_F32: return launch_persistent<128, 6, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
     }
   }
   return GB_ERR_ARG;

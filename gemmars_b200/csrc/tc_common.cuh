@@ -2,8 +2,9 @@
 //
 // Device side: inline PTX for mbarriers (with a bounded wait), TMA tile loads, tensor memory
 // and tcgen05.mma, and the shared-memory matrix descriptor of a K-major, 128-byte-swizzled
-// tile.  Host side: tensor maps for row-major bfloat16 matrices cut into [rows, 64] boxes,
-// encoded through the driver entry point (no link against libcuda) and remembered by key.
+// tile.  Host side: tensor maps for row-major bfloat16 matrices cut into [rows, 64] boxes and for
+// result matrices, encoded through the driver entry point (no link against libcuda) and
+// remembered by key.
 // No load here uses cluster multicast.
 #pragma once
 
@@ -51,6 +52,24 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// A tile of shared memory to global memory through a tensor map: stored, or added (the map's type:
+// float32).  The requests of a thread form groups; tma_store_wait_read<N> returns when all but the
+// last N groups have been read out of shared memory, tma_store_wait_all when they are all written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// What this thread wrote to shared memory becomes visible to TMA (the asynchronous proxy).
+__device__ __forceinline__ void fence_smem_to_tma() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint64_t* bar) {
@@ -123,25 +142,25 @@ EncodeTiled encode_fn() {
 struct MapKey {
   const void* base;
   uint64_t rows, cols, pitch;
-  uint32_t box_rows;
+  uint32_t box_rows, kind;
   bool operator==(const MapKey& o) const {
-    return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows;
+    return base == o.base && rows == o.rows && cols == o.cols && pitch == o.pitch && box_rows == o.box_rows && kind == o.kind;
   }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
     size_t h = (size_t)k.base;
-    for (uint64_t v : {k.rows, k.cols, k.pitch, (uint64_t)k.box_rows}) h = h * 1000003u ^ (size_t)v;
+    for (uint64_t v : {k.rows, k.cols, k.pitch, (uint64_t)k.box_rows, (uint64_t)k.kind}) h = h * 1000003u ^ (size_t)v;
     return h;
   }
 };
 
-// A [rows, cols] bfloat16 matrix with rows `pitch` bytes apart, cut into [box_rows, 64] boxes.
 // Maps are remembered: weights and reused activation buffers are encoded once.
-bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows) {
+bool tensor_map_any(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows,
+                    uint32_t box_cols, CUtensorMapDataType type, CUtensorMapSwizzle swizzle, uint32_t kind) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex mu;
-  MapKey key{base, rows, cols, pitch, box_rows};
+  MapKey key{base, rows, cols, pitch, box_rows, kind};
   std::lock_guard<std::mutex> lock(mu);
   auto it = cache.find(key);
   if (it != cache.end()) {
@@ -152,15 +171,34 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
   if (!fn) return false;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {pitch};
-  cuuint32_t box[2] = {TC_BOX_COLS, box_rows};
+  cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t elem[2] = {1, 1};
-  if (fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+  if (fn(out, type, 2, const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return false;
   if (cache.size() > 65536) cache.clear();
   cache.emplace(key, *out);
   return true;
+}
+
+// A [rows, cols] bfloat16 matrix with rows `pitch` bytes apart, cut into [box_rows, 64] boxes
+// (operands of the products: 128-byte swizzle).
+bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t box_rows) {
+  return tensor_map_any(out, base, rows, cols, pitch, box_rows, TC_BOX_COLS, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                        CU_TENSOR_MAP_SWIZZLE_128B, 0);
+}
+
+// A [rows, cols] result matrix (bfloat16 or float32) written in [piece_rows, TC_OUT_COLS] pieces
+// (piece_rows up to TC_OUT_ROWS) that lie row after row in shared memory.  False when TMA cannot
+// address it (base and pitch must be multiples of 16 bytes): the caller then stores with plain
+// instructions.
+constexpr int TC_OUT_ROWS = 32, TC_OUT_COLS = 32;
+bool tensor_map_out(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t piece_rows,
+                    bool f32) {
+  if (((uintptr_t)base & 15) || (pitch & 15) || piece_rows > (uint32_t)TC_OUT_ROWS) return false;
+  return tensor_map_any(out, base, rows, cols, pitch, piece_rows, TC_OUT_COLS,
+                        f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, f32 ? 2 : 1);
 }
 
 }  // namespace
