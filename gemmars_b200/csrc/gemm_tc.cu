@@ -103,32 +103,28 @@ constexpr int PIECE_BYTES = PIECE_TOKENS * PIECE_FEATURES * 4;          // float
 constexpr int PIECES = 2;                                               // pieces of a warp in flight
 constexpr int OUT_STAGING_BYTES = 4 * PIECES * PIECE_BYTES;             // four warps
 
-template <int MODE>
+template <int MODE, int SLOT_BYTES = PIECE_BYTES>
 struct TileOut {
+  static constexpr int FEATURES = PIECE_FEATURES;
   const CUtensorMap* map;
   uint8_t* pieces;   // this warp's pieces, 128-byte aligned
   uint32_t sent;
   __device__ __forceinline__ TileOut(const CUtensorMap* m, uint8_t* staging, int warp)
-      : map(m), pieces(staging + warp * PIECES * PIECE_BYTES), sent(0) {}
+      : map(m), pieces(staging + warp * PIECES * SLOT_BYTES), sent(0) {}
   __device__ __forceinline__ static void put(uint8_t* p, int token, int lane, float r) {
-    if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16) ((bf16*)p)[token * PIECE_FEATURES + lane] = __float2bfloat16_rn(r);
-    else ((float*)p)[token * PIECE_FEATURES + lane] = r;
+    if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16) ((bf16*)p)[token * FEATURES + lane] = __float2bfloat16_rn(r);
+    else ((float*)p)[token * FEATURES + lane] = r;
   }
-  // lo, hi: tokens 0-15 and (with `both`) 16-31 of this lane's feature; x: the warp's first
-  // feature; row: the first token.  The map's pieces are 32 tokens long with `both`, else 16.
-  __device__ __forceinline__ void send(const uint32_t (&lo)[16], const uint32_t (&hi)[16], bool both, float bias, int lane,
-                                       int x, int row, int N) {
-    uint8_t* p = pieces + (sent % PIECES) * PIECE_BYTES;
-    if (sent >= PIECES) {   // the piece sent PIECES calls ago has left this memory
+  // the piece to fill next; waits until the request that last used its memory has read it
+  __device__ __forceinline__ uint8_t* next(int lane) {
+    if (sent >= PIECES) {
       if (lane == 0) tma_store_wait_read<PIECES - 1>();
       __syncwarp();
     }
-#pragma unroll
-    for (int j = 0; j < 16; ++j) put(p, j, lane, __uint_as_float(lo[j]) + bias);
-    if (both) {
-#pragma unroll
-      for (int j = 0; j < 16; ++j) put(p, 16 + j, lane, __uint_as_float(hi[j]) + bias);
-    }
+    return pieces + (sent % PIECES) * SLOT_BYTES;
+  }
+  // after every lane has put its values: one request for the whole piece
+  __device__ __forceinline__ void post(uint8_t* p, int lane, int x, int row, int N) {
     fence_smem_to_tma();
     __syncwarp();
     if (lane == 0 && x < N) {
@@ -137,6 +133,19 @@ struct TileOut {
       tma_store_commit();
     }
     ++sent;
+  }
+  // lo, hi: tokens 0-15 and (with `both`) 16-31 of this lane's feature; x: the warp's first
+  // feature; row: the first token.  The map's pieces are 32 tokens long with `both`, else 16.
+  __device__ __forceinline__ void send(const uint32_t (&lo)[16], const uint32_t (&hi)[16], bool both, float bias, int lane,
+                                       int x, int row, int N) {
+    uint8_t* p = next(lane);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) put(p, j, lane, __uint_as_float(lo[j]) + bias);
+    if (both) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) put(p, 16 + j, lane, __uint_as_float(hi[j]) + bias);
+    }
+    post(p, lane, x, row, N);
   }
   // before the shared memory is given up and the kernel ends
   __device__ __forceinline__ void finish(int lane) {
@@ -180,6 +189,33 @@ __device__ __forceinline__ void gate(uint32_t (&v)[16], const uint32_t (&u)[16])
     for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(silu_mul(__uint_as_float(v[j]), __uint_as_float(u[j])));
   }
 }
+
+// The gated product of the persistent kernel keeps gate and up rows of W in one tile of 128 rows:
+// 64 gate rows, then the up rows of the same 64 features.  Epilogue warps 0 and 1 then hold gate
+// values (32 features each, one per lane), warps 2 and 3 the up values of the same features, and
+// warp w and w + 2 are a pair: of 32 tokens the gate warp finishes the first 16 and the up warp
+// the last 16, each handing the other, through shared memory, the 16 values it lacks (of 16
+// tokens the gate warp finishes all).  GateExchange is one pair's memory: two rounds (a warp
+// writes round r + 2 only after the pair's barrier of round r + 1, which its partner reaches
+// after it has read round r), two directions, 16 tokens x 32 lanes of float32.
+constexpr int EXCHANGE_BYTES = 2 * 2 * 2 * 16 * 32 * 4;   // two pairs
+struct GateExchange {
+  float* base;      // this pair's [round & 1][direction][16][32]
+  uint32_t round;
+  int pair;
+  __device__ __forceinline__ GateExchange(uint8_t* mem, int warp) : base((float*)mem + (warp & 1) * 2 * 2 * 16 * 32), round(0), pair(warp & 1) {}
+  // give: the 16 values of this lane that the partner finishes; returns in `got` the partner's
+  __device__ __forceinline__ void swap(const uint32_t (&give)[16], bool is_up, int lane, uint32_t (&got)[16]) {
+    float* mine = base + ((round & 1) * 2 + (is_up ? 1 : 0)) * 16 * 32;
+    const float* theirs = base + ((round & 1) * 2 + (is_up ? 0 : 1)) * 16 * 32;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) mine[j * 32 + lane] = __uint_as_float(give[j]);
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+#pragma unroll
+    for (int j = 0; j < 16; ++j) got[j] = __float_as_uint(theirs[j * 32 + lane]);
+    ++round;
+  }
+};
 
 // One value of one token of one head tile, held by epilogue thread f = feature; all 128 epilogue
 // threads call it together.  red: 4 floats, xs: 128 floats of shared memory.
@@ -472,19 +508,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // share the same rows of W).  The accumulator in tensor memory is double-buffered: while the
 // four epilogue warps read tile i out of one buffer and store it, the MMA warp already fills the
 // other with tile i + 1, and the TMA warp runs ahead through the shared-memory stages across
-// tile borders.  Gated mode keeps two accumulators per buffer (BN <= 128).
+// tile borders.  In gated mode a tile's 128 rows of W are 64 gate rows and the 64 up rows of the same
+// features, and the tile gives 64 features of the result: one accumulator and as
+// many shared-memory bytes per MMA cycle as the plain product (two accumulators over 128 tokens
+// read the tokens twice and ran at 735 cycles a block of 64 inner elements, against 547).
 // Tile t of the walk: token tiles come in groups of 2,048 tokens; inside a group the token tile
 // runs fastest and the feature tile slowest, and the groups follow one another.  The CTAs that run
 // together then share a few rows of W and one group's rows of x (16 MB at 4,096 wide), which stay
 // in L2 while W streams past once per group; with the token tile fastest over all tokens, a
 // 16,384-token step read x again for every feature tile (measured: 2.5 GB from memory for the
 // q/k/v product, whose operands are 0.18 GB).
-__device__ __forceinline__ void tile_origin(int t, int tiles_m, int tiles_n, int bn, int& m0, int& n0) {
+__device__ __forceinline__ void tile_origin(int t, int tiles_m, int tiles_n, int bn, int tile_features, int& m0, int& n0) {
   const int group = max(1, 2048 / bn), per_group = group * tiles_n;
   const int g = t / per_group, r = t - g * per_group;
   const int gm = min(group, tiles_m - g * group);
   m0 = (g * group + r % gm) * bn;
-  n0 = (r / gm) * BM;
+  n0 = (r / gm) * tile_features;
 }
 
 #ifdef GB_TRACE
@@ -499,10 +538,11 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
                           void* __restrict__ y, int M, int N, int K, long long ldy, int bn) {
-  constexpr bool DUAL = MODE == EPI_SWIGLU_BF16;
-  constexpr uint32_t W_BYTES = BM * BK * 2, A_BYTES = (DUAL ? 2 : 1) * W_BYTES, B_BYTES = BN * BK * 2;
+  constexpr bool GATED = MODE == EPI_SWIGLU_BF16;   // rows of a tile: 16 gate, 16 up, ... (see gate_rows)
+  constexpr int TILE_F = GATED ? BM / 2 : BM;       // features of the result per tile
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t ACC_COLS = (DUAL ? 2 : 1) * BN, TMEM_COLS = 2 * ACC_COLS;
+  constexpr uint32_t ACC_COLS = BN, TMEM_COLS = 2 * ACC_COLS;
   static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "two accumulator buffers: 256 or 512 columns");
   // bn: tokens per tile, a multiple of 16 up to BN (BN sizes the stages and the accumulators)
   const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -515,9 +555,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   uint64_t* acc_empty = acc_full + 2;          // 2: the epilogue warps have read it out
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   uint8_t* out_staging = smem + STAGES * STAGE_BYTES + 1024;   // past the barriers; OUT_STAGING_BYTES
+  // gated: the pieces are 16 tokens of bfloat16 (1 KB), and the pairs' exchange has the upper half
+  constexpr int SLOT = GATED ? OUT_STAGING_BYTES / 2 / (4 * PIECES) : PIECE_BYTES;
+  static_assert(!GATED || (SLOT >= 16 * PIECE_FEATURES * 2 && OUT_STAGING_BYTES / 2 >= EXCHANGE_BYTES), "gated staging");
+  __shared__ int epilogue_gave_up;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + bn - 1) / bn, tiles_n = (N + BM - 1) / BM, tiles = tiles_m * tiles_n;
+  const int tiles_m = (M + bn - 1) / bn, tiles_n = (N + TILE_F - 1) / TILE_F, tiles = tiles_m * tiles_n;
   const int kb_total = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -529,6 +573,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 4);
     }
+    epilogue_gave_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -550,7 +595,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       bool ok = true;
       for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
         int m0, n0;
-        tile_origin(t, tiles_m, tiles_n, bn, m0, n0);
+        tile_origin(t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
@@ -561,8 +606,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           uint8_t* a = smem + s * STAGE_BYTES;
           PTRACE(it, 0);   // producer: stage free, loading block `it`
           mbar_expect_tx(&full_bar[s], stage_tx);
-          tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
-          if (DUAL) tma_load_2d(a + W_BYTES, &map_w, kb * BK, N + n0, &full_bar[s]);
+          if (GATED) {   // map_w is cut into boxes of 64 rows: the gate rows, then the same features' up rows
+            // (a request costs the issuing thread about 75 cycles: boxes of 16 rows, which would let a
+            // warp gate without shared memory, made nine requests a block and the producer the limit)
+            tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
+            tma_load_2d(a + A_BYTES / 2, &map_w, kb * BK, N + n0, &full_bar[s]);
+          } else {
+            tma_load_2d(a, &map_w, kb * BK, n0, &full_bar[s]);
+          }
           tma_load_2d(a + A_BYTES, &map_x, kb * BK, m0, &full_bar[s]);
         }
       }
@@ -592,12 +643,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           tc_fence_after();
           PTRACE(it, 1);   // MMA: block `it` has arrived
           const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
-          const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES), udesc = smem_desc(a + W_BYTES);
+          const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
+          for (int k = 0; k < BK / UMMA_K; ++k)
             tc_mma(d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            if (DUAL) tc_mma(d + BN, udesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
           tc_commit(&empty_bar[s]);
           PTRACE(it, 2);   // MMA: block `it` issued
         }
@@ -608,19 +657,25 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   } else {
     // ---------------- epilogue warps: lane = feature, column = token
     pdl_wait_prior();
-    const int f = warp * 32 + lane;
-    TileOut<MODE> tile_out(&map_y, out_staging, warp);
+    const int f = GATED ? (warp & 1) * 32 + lane : warp * 32 + lane;   // this lane's feature of the tile
+    const bool is_up = GATED && warp >= 2;
+    TileOut<MODE, SLOT> tile_out(&map_y, out_staging, warp);
+    GateExchange exchange(out_staging + OUT_STAGING_BYTES / 2, warp);
     const bool both = bn % 32 == 0;   // 32 tokens per round; the result's map is cut to match
     uint32_t i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
       const uint32_t b = i & 1;
       int m0, n0;
-      tile_origin(t, tiles_m, tiles_n, bn, m0, n0);
+      tile_origin(t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
       const int n = n0 + f;
-      if (!__all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1))) {
-        if (lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
-        break;
+      bool have = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1));
+      if (!have && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
+      if (GATED) {   // the warps of a pair meet at barriers below: they leave together or not at all
+        if (!have && lane == 0) epilogue_gave_up = 1;
+        asm volatile("bar.sync 3, 128;" ::: "memory");
+        have = epilogue_gave_up == 0;
       }
+      if (!have) break;
       tc_fence_after();
       if (threadIdx.x == 0) PTRACE(i, 3);   // epilogue: tile i complete
       const float bv = (bias && n < N) ? bias[n] : 0.f;
@@ -628,13 +683,34 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 #pragma unroll 1
       for (int c = 0; c < bn; c += both ? 32 : 16) {
         if (m0 + c >= M) break;
-        uint32_t v[16], u[16], v2[16], u2[16];
-        acc_load<DUAL>(acc, BN, c, v, u);
-        if (both) acc_load<DUAL>(acc, BN, c + 16, v2, u2);
+        uint32_t v[16], v2[16];
+        tc_ld16(acc + c, v);
+        if (both) tc_ld16(acc + c + 16, v2);
         tc_wait_ld();
-        gate<DUAL>(v, u);
-        if (both) gate<DUAL>(v2, u2);
-        if (y_tma) {
+        if (GATED) {
+          // 32 tokens: the gate warp gives its last 16 and finishes the first 16, the up warp the other
+          // way round; 16 tokens: the up warp gives, the gate warp finishes
+          uint32_t got[16];
+          exchange.swap((both && !is_up) ? v2 : v, is_up, lane, got);
+          if (both || !is_up) {
+            const uint32_t (&g)[16] = is_up ? got : v;
+            const uint32_t (&u)[16] = is_up ? v2 : got;
+            const int row = m0 + c + (is_up ? 16 : 0);
+            float r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = silu_mul(__uint_as_float(g[j]), __uint_as_float(u[j]));
+            if (y_tma) {
+              uint8_t* p = tile_out.next(lane);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) tile_out.put(p, j, lane, r[j]);
+              tile_out.post(p, lane, n0 + (warp & 1) * 32, row, N);
+            } else if (n < N) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (row + j < M) emit<MODE>(y, (size_t)(row + j) * ldy + n, r[j]);
+            }
+          }
+        } else if (y_tma) {
           tile_out.send(v, v2, both, bv, lane, n0 + warp * 32, m0 + c, N);
         } else {
           store_direct<MODE>(y, ldy, v, bv, m0 + c, M, n, N);
@@ -666,7 +742,7 @@ OutMap out_map(const void* y, int mode, int M, int N, long long ldy, int bn) {
   OutMap o = {};
   const bool f32 = mode == EPI_STORE_F32 || mode == EPI_ACCUMULATE_F32;
   o.usable = mode != EPI_QKV_BF16 && tensor_map_out(&o.map, y, (uint64_t)M, (uint64_t)N, (uint64_t)ldy * (f32 ? 4 : 2),
-                                                    bn % 32 == 0 ? 32 : 16, f32);
+                                                    bn % 32 == 0 ? 32 : 16, 32, f32);
   return o;
 }
 
@@ -717,11 +793,11 @@ int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const Ou
 template <int BN, int STAGES, int MODE>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
                       int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream) {
-  constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
   // stages, 1 KB of barriers, the pieces on their way out, 1 KB to align the base
-  constexpr size_t SMEM = (size_t)STAGES * ((size_t)NW * BM * BK * 2 + BN * BK * 2) + 1024 + OUT_STAGING_BYTES + 1024;
-  static_assert((2 * STAGES + 4) * 8 + 16 <= 1024, "the barriers have 1 KB");
+  constexpr size_t SMEM = (size_t)STAGES * ((size_t)BM * BK * 2 + BN * BK * 2) + 1024 + OUT_STAGING_BYTES + 1024;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
+  static_assert((2 * STAGES + 4) * 8 + 16 <= 1024, "the barriers have 1 KB");
+  constexpr int TILE_F = MODE == EPI_SWIGLU_BF16 ? BM / 2 : BM;
   auto kernel = gemm_tc_persistent_kernel<BN, STAGES, MODE>;
   static bool configured = false;
   if (!configured) {
@@ -729,7 +805,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
       return (int)cudaGetLastError();
     configured = true;
   }
-  const int tiles = ((M + bn - 1) / bn) * ((N + BM - 1) / BM);
+  const int tiles = ((M + bn - 1) / bn) * ((N + TILE_F - 1) / TILE_F);
   gb_launch(kernel, dim3(tiles < ctas ? tiles : ctas), dim3(THREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N,
             K, ldy, bn);
   return gb_launch_status();
@@ -816,7 +892,7 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, const float* bias, vo
 
 // The same product for prompts (M > 64): one CTA per SM walks the tiles and the epilogue of a tile
 // runs under the MMAs of the next.  mode as gb_gemm_tc; bn: tokens per tile, a multiple of 16 up to
-// 256 (gated: 128); ctas: CTAs to launch.
+// 256; ctas: CTAs to launch.
 GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N,
                                     int K, long long ldx, long long ldy, int bn, int ctas, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
@@ -825,12 +901,13 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
   const bool swiglu = mode == EPI_SWIGLU_BF16;
   if (swiglu && bias) return GB_ERR_ARG;
   CUtensorMap mw, mx;
-  if (!tensor_map(&mw, w, (uint64_t)N * (swiglu ? 2 : 1), (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
+  // gated: W in boxes of 64 rows; a tile is 64 gate rows and the same features' 64 up rows
+  if (!tensor_map(&mw, w, (uint64_t)N * (swiglu ? 2 : 1), (uint64_t)K, (uint64_t)K * 2, swiglu ? BM / 2 : BM)) return GB_ERR_ARG;
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
-  const OutMap my = out_map(y, mode, M, N, ldy, bn);
+  const OutMap my = out_map(y, mode, M, N, ldy, swiglu ? 16 : bn);   // gated: a warp sends 16 tokens at a time
   if (swiglu) {
-    if (bn > 128) return GB_ERR_SIZE;
-    return launch_persistent<128, 4, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+    if (bn > 128) return launch_persistent<256, 4, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+    return launch_persistent<128, 6, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
   }
   if (bn > 128) {
     switch (mode) {

@@ -188,17 +188,19 @@ bool tensor_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
                         CU_TENSOR_MAP_SWIZZLE_128B, 0);
 }
 
-// A [rows, cols] result matrix (bfloat16 or float32) written in [piece_rows, TC_OUT_COLS] pieces
-// (piece_rows up to TC_OUT_ROWS) that lie row after row in shared memory.  False when TMA cannot
-// address it (base and pitch must be multiples of 16 bytes): the caller then stores with plain
-// instructions.
+// A [rows, cols] result matrix (bfloat16 or float32) written in [piece_rows, piece_cols] pieces
+// (up to TC_OUT_ROWS x TC_OUT_COLS) that lie row after row in shared memory.  False when TMA
+// cannot address it (base and pitch must be multiples of 16 bytes): the caller then stores with
+// plain instructions.
 constexpr int TC_OUT_ROWS = 32, TC_OUT_COLS = 32;
 bool tensor_map_out(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t pitch, uint32_t piece_rows,
-                    bool f32) {
-  if (((uintptr_t)base & 15) || (pitch & 15) || piece_rows > (uint32_t)TC_OUT_ROWS) return false;
-  return tensor_map_any(out, base, rows, cols, pitch, piece_rows, TC_OUT_COLS,
+                    uint32_t piece_cols, bool f32) {
+  if (((uintptr_t)base & 15) || (pitch & 15) || piece_rows > (uint32_t)TC_OUT_ROWS || piece_cols > (uint32_t)TC_OUT_COLS ||
+      (piece_cols * (f32 ? 4 : 2)) % 16)
+    return false;
+  return tensor_map_any(out, base, rows, cols, pitch, piece_rows, piece_cols,
                         f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, f32 ? 2 : 1);
+                        CU_TENSOR_MAP_SWIZZLE_NONE, (f32 ? 2 : 1) | (piece_cols << 4));
 }
 
 }  // namespace

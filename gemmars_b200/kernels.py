@@ -292,7 +292,7 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == n
     if bn is None:
-        bn = 128 if (swiglu or m <= 128) else 256
+        bn = 128 if m <= 128 else 256
     f = _fn("gemm_tc", "gb_gemm_tc_persistent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
              c_int, c_void_p])
