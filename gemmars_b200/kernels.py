@@ -292,6 +292,8 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == n
     if bn is None:
+        # 256 tokens a tile; narrower tiles that fill the last round better (240 tokens for 2,048 x 4,096)
+        # were 1.5 % faster alone and 4 % slower inside a prompt step
         bn = 128 if m <= 128 else 256
     f = _fn("gemm_tc", "gb_gemm_tc_persistent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
