@@ -70,7 +70,11 @@ __device__ __forceinline__ void trace(int slot) {
   const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   if (cta < 4096) g_trace[cta * 8 + slot] = t;
 }
+#ifdef GB_TRACE_MODE   // only the kernels of one epilogue mode record (the last such launch stays)
+#define TRACE(slot) do { if (MODE == GB_TRACE_MODE) trace(slot); } while (0)
+#else
 #define TRACE(slot) trace(slot)
+#endif
 #else
 #define TRACE(slot)
 #endif
@@ -371,7 +375,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
 
   // ---------------- epilogue (warps 0-3); the other warps wait at the barriers below
-  float* partial = (float*)smem;   // [ACC_COLS][BM] float32, over the pipeline stages (idle by then)
   bool have_acc = false;
   // with the inner dimension split, every rank adds a share of the tile's real tokens over all ranks
   const int real = min(M - m0, BN), share = (real + (int)nsplit - 1) / (int)nsplit;
@@ -394,75 +397,85 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     if (threadIdx.x == 0) TRACE(4);
   }
   if (nsplit > 1) {
-    // every rank publishes its partial sums, then adds its share of the tokens in rank order
+    // Every rank sends each token's partial sums to the rank that finishes the token, into that
+    // rank's shared memory (remote stores do not wait for an answer), and after one cluster
+    // barrier every rank adds what it received, in rank order, from its own shared memory.
+    // (Publishing in place and reading the other ranks' memory cost a round trip per token and a
+    // second barrier before anyone could leave: 4.1 us from the last MMA to the last store with
+    // eight ranks, measured inside a decode step.)  The memory is the pipeline's stages, so a rank
+    // may be written to only when its MMAs are done: that is the first barrier, which every
+    // thread arrives at as soon as this rank's accumulator is complete.
+    float* recv = (float*)smem;   // [rank][token of this rank's share][accumulator][BM]
+    constexpr int NACC = DUAL ? 2 : 1;
+    cluster_arrive();
+    cluster_wait();
     if (warp < 4) {
       const int f = warp * 32 + lane;
+      const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16);
+      int owner = 0, local = 0;   // of token c + j
 #pragma unroll 1
-      for (int c = 0; c < (int)ACC_COLS; c += 16) {
-        if ((c % BN) >= real) continue;
-        uint32_t v[16];
+      for (int c = 0; c < BN && c < real; c += 16) {
+        uint32_t v[16], u[16];
         if (have_acc) {
-          tc_ld16(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+          acc_load<DUAL>(acc, BN, c, v, u);
           tc_wait_ld();
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = 0u;
+          for (int j = 0; j < 16; ++j) v[j] = u[j] = 0u;
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) partial[(c + j) * BM + f] = __uint_as_float(v[j]);
+        for (int j = 0; j < 16; ++j) {
+          if (c + j < real) {
+            float* slot = recv + ((size_t)((int)split * share + local) * NACC) * BM + f;
+            st_peer_f32(slot, (uint32_t)owner, __uint_as_float(v[j]));
+            if (DUAL) st_peer_f32(slot + BM, (uint32_t)owner, __uint_as_float(u[j]));
+            if (++local == share) {
+              local = 0;
+              ++owner;
+            }
+          }
+        }
       }
     }
     cluster_sync();
     if (threadIdx.x == 0) TRACE(5);
     if (warp < 4) {
       const int f = warp * 32 + lane, n = n0 + f;
-      constexpr int CH = DUAL ? 2 : 4;   // tokens whose loads are in flight together (8 ranks each)
 #pragma unroll 1
-      for (int base = c0; base < c1; base += CH) {
-        float v[CH][8], u[CH][8];
+      for (int c = c0; c < c1; ++c) {
+        const float* mine = recv + ((size_t)(c - c0) * NACC) * BM + f;
+        const size_t rank_stride = (size_t)share * NACC * BM;
+        float part[8], part_up[8];
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-          const int c = min(base + i, c1 - 1);
-#pragma unroll
-          for (uint32_t r = 0; r < 8; ++r) {
-            v[i][r] = r < nsplit ? ld_peer_f32(&partial[c * BM + f], r) : 0.f;
-            if (DUAL) u[i][r] = r < nsplit ? ld_peer_f32(&partial[(BN + c) * BM + f], r) : 0.f;
-          }
+        for (uint32_t r = 0; r < 8; ++r) {
+          part[r] = r < nsplit ? mine[r * rank_stride] : 0.f;
+          if (DUAL) part_up[r] = r < nsplit ? mine[r * rank_stride + BM] : 0.f;
         }
+        float sum = part[0];
 #pragma unroll
-        for (int i = 0; i < CH; ++i) {
-          const int c = base + i;
-          if (MODE == EPI_QKV_BF16) {
-            if (c >= c1) continue;   // the same for every thread: they finish a token together
-            float head_v = v[i][0];
+        for (int r = 1; r < 8; ++r) sum += part[r];
+        if (MODE == EPI_QKV_BF16) {   // every thread has the same tokens: they finish one together
+          qkv_finish(tail, y, ldy, m0 + c, n0, f, sum + bias_v, qkv_red, qkv_xs);
+          continue;
+        }
+        if (n >= N) continue;
+        if (DUAL) {
+          float up = part_up[0];
 #pragma unroll
-            for (int r = 1; r < 8; ++r) head_v += v[i][r];
-            qkv_finish(tail, y, ldy, m0 + c, n0, f, head_v + bias_v, qkv_red, qkv_xs);
-            continue;
-          }
-          if (c >= c1 || n >= N) continue;
-          float acc = v[i][0];
+          for (int r = 1; r < 8; ++r) up += part_up[r];
+          sum = silu_mul(sum, up);
+        }
+        const size_t idx = (size_t)(m0 + c) * ldy + n;
+        if (MODE == EPI_ACCUMULATE_F32) {
+          float prev = c - c0 < 8 ? 0.f : ((const float*)y)[idx];   // the first eight were asked for early
 #pragma unroll
-          for (int r = 1; r < 8; ++r) acc += v[i][r];
-          if (DUAL) {
-            float up = u[i][0];
-#pragma unroll
-            for (int r = 1; r < 8; ++r) up += u[i][r];
-            acc = silu_mul(acc, up);
-          }
-          const size_t idx = (size_t)(m0 + c) * ldy + n;
-          if (MODE == EPI_ACCUMULATE_F32) {
-            float prev = 0.f;   // old[c - c0] without indexing registers by a variable
-#pragma unroll
-            for (int q = 0; q < 8; ++q) prev = (c - c0 == q) ? old[q] : prev;
-            ((float*)y)[idx] = prev + acc + bias_v;
-          } else {
-            emit<MODE>(y, idx, acc + bias_v);
-          }
+          for (int q = 0; q < 8; ++q) prev = (c - c0 == q) ? old[q] : prev;
+          ((float*)y)[idx] = prev + sum + bias_v;
+        } else {
+          emit<MODE>(y, idx, sum + bias_v);
         }
       }
     }
-    cluster_sync();  // every rank keeps its shared memory until the others have read it
   } else if (warp < 4 && have_acc) {
     const int f = warp * 32 + lane, n = n0 + f;
     const float b = bias_v;
@@ -753,7 +766,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const
   constexpr size_t STAGE = (size_t)NW * BM * BK * 2 + BN * BK * 2;
   constexpr size_t SMEM = (size_t)STAGES * STAGE + (2 * STAGES + 1) * 8 + 16 + 1024;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
-  static_assert(BN > 64 || (size_t)NW * BN * BM * 4 <= (size_t)STAGES * STAGE, "partial sums need the stage memory");
+  static_assert(BN > 64 || (size_t)NW * (BN + 8) * BM * 4 <= (size_t)STAGES * STAGE, "the ranks' partial sums need the stage memory");
   static_assert((size_t)OUT_STAGING_BYTES <= (size_t)STAGES * STAGE, "the pieces on their way out need the stage memory");
   auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
   static bool configured = false;

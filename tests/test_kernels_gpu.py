@@ -87,6 +87,11 @@ def test_gemm_tc_cluster_split(k, splits):
         again = torch.zeros_like(out)
         k.gemm_tc(x, w, again, bn=bn, splits=splits)
         assert torch.equal(out, again)                      # added in rank order: the same bits every run
+        # added into a residual: every token of a rank's share keeps what was there (shares of
+        # more than eight tokens with two and four ranks)
+        acc = torch.full((m, 333), 3.0, device="cuda")
+        k.gemm_tc(x, w, acc, accumulate=True, bn=bn, splits=splits)
+        assert (acc - (ref + 3.0)).abs().max().item() <= 1e-5 * (ref.abs().max().item() + 3.0)
     assert k.gemm_tc_status() == 0
 
 
