@@ -9,12 +9,15 @@
 // are, so TMA brings [128 x 64] tiles of W and [BN x 64] tiles of x into 128-byte-swizzled
 // shared memory, one elected thread issues tcgen05.mma with the accumulator in tensor memory
 // (lane = feature, column = token), and four warps read it back with tcgen05.ld: for one
-// token, the 32 lanes of a warp hold 32 consecutive features, so stores are coalesced.
+// token, the 32 lanes of a warp hold 32 consecutive features.  A result that TMA can address
+// leaves as TMA stores of 32 tokens x 32 features staged in shared memory (TileOut), any other
+// with plain stores.
 //
 // Two kernels.  gemm_tc_kernel, one tile per CTA, serves decoding (BN = 16..64, where the CTA
 // only streams its rows of W at memory speed): when that leaves too few tiles for the 148 SMs,
-// the inner dimension is split over the CTAs of a thread-block cluster, whose partial sums are
-// added in rank order through distributed shared memory: no atomics, the same bits every run.
+// the inner dimension is split over the CTAs of a thread-block cluster, whose partial sums meet
+// in the shared memory of the rank that finishes the token and are added there in rank order:
+// no atomics, the same bits every run.
 // gemm_tc_persistent_kernel serves prompts (BN = 128 or 256): one CTA per SM walks the tiles
 // with two accumulator buffers, so a tile's epilogue runs under the next tile's MMAs.
 //
@@ -32,9 +35,10 @@ constexpr int BK = 64;           // inner elements per stage: 64 bf16 = one 128-
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 
-// EPI_SWIGLU_BF16: W stacks a gate matrix over an up matrix ([2N, K]); the CTA keeps two
-// accumulators (gate rows and up rows of the same 128 features against one tile of x) and
-// writes silu(gate) * up in bfloat16, so the [M, 2N] intermediate never exists.
+// EPI_SWIGLU_BF16: W stacks a gate matrix over an up matrix ([2N, K]) and the kernel writes
+// silu(gate) * up in bfloat16, so the [M, 2N] intermediate never exists.  gemm_tc_kernel keeps two
+// accumulators (gate rows and up rows of the same 128 features against one tile of x);
+// gemm_tc_persistent_kernel one, whose 128 rows are 64 gate rows and the same features' up rows.
 enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2, EPI_SWIGLU_BF16 = 3, EPI_QKV_BF16 = 4 };
 
 // EPI_QKV_BF16: the q/k/v product of a decode step whose head size is the tile's 128 features: a
