@@ -428,7 +428,9 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
   float acc[MERGE_EPT];
 #pragma unroll
   for (int e = 0; e < MERGE_EPT; ++e) acc[e] = 0.f;
-  constexpr int AHEAD = 8;   // parts of the thread's first value asked for before the factors are known
+  // parts of the thread's first value asked for before the factors are known: a lone sequence of
+  // 8,192 tokens is cut into about 19 parts per kv head, which then come in one round trip
+  constexpr int AHEAD = 24;
   for (int base = 0; base < n; base += MERGE_ROUND) {
     const int cn = min(MERGE_ROUND, n - base);
     __syncthreads();
