@@ -67,20 +67,25 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_
 struct TokenSpan {
   int slot, lo, hi, first_page, pages;
 };
+// A token whose slot is skip_slot belongs to no sequence (a row that pads a captured step): it
+// asks for nothing and its row of the result is zero.  (Left in, 8 such rows x 8 kv heads
+// were 64 one-page segments at the end of the list, all in the last CTA's range, and made a step
+// of 24 sequences slower than one of 32.)
 __device__ __forceinline__ TokenSpan token_span(int t, const int* tok_pos, const int* tok_seq, const int* seq_slot,
-                                               int window) {
+                                               int window, int skip_slot) {
   TokenSpan s;
   const int pos = tok_pos[t];
   s.slot = seq_slot[tok_seq[t]];
   s.hi = pos + 1;
   s.lo = window > 0 ? max(0, s.hi - window) : 0;
   s.first_page = s.lo / KEYS;
-  s.pages = (s.hi - 1) / KEYS - s.first_page + 1;
+  s.pages = s.slot == skip_slot ? 0 : (s.hi - 1) / KEYS - s.first_page + 1;
   return s;
 }
 
 // The flat list of pages: token t's pages of kv head h start at (prefix[t] * nkv + h * pages_t).
-// Finds the token that flat index p falls into (prefix is non-decreasing, prefix[ntok] * nkv > p).
+// Finds the token that flat index p falls into (prefix is non-decreasing, prefix[ntok] * nkv > p):
+// the last token whose pages start at or before p, which is never a token without pages.
 __device__ __forceinline__ int token_of(const int* prefix, int ntok, int nkv, long long p) {
   int lo = 0, hi = ntok - 1;
   while (lo < hi) {
@@ -98,7 +103,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
                                const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out,
                                long long out_stride, const int* __restrict__ page_table, int table_width, int nkv,
                                const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                               const int* __restrict__ seq_slot, int ntok, int nh, int window,
+                               const int* __restrict__ seq_slot, int ntok, int nh, int window, int skip_slot,
                                float* __restrict__ part, int* __restrict__ prefix_out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -121,7 +126,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
   // Positions, slots and the page table are the step's inputs, not the work of the kernel before
   // this one: the lists of pages are made before waiting for it; q and the cache are read after.
   // ---- pages per token, then their running sum (warp 0, 32 tokens a round)
-  for (int t = threadIdx.x; t < ntok; t += THREADS) prefix[t + 1] = token_span(t, tok_pos, tok_seq, seq_slot, window).pages;
+  for (int t = threadIdx.x; t < ntok; t += THREADS) prefix[t + 1] = token_span(t, tok_pos, tok_seq, seq_slot, window, skip_slot).pages;
   __syncthreads();
   if (warp == 0) {
     int carry = 0;
@@ -153,7 +158,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     auto lookup = [&](long long p) -> int {   // row of the cache (page * nkv + kv head) of flat page p
       if (p >= p1) return 0;
       const int t = token_of(prefix, ntok, nkv, p);
-      const TokenSpan sp = token_span(t, tok_pos, tok_seq, seq_slot, window);
+      const TokenSpan sp = token_span(t, tok_pos, tok_seq, seq_slot, window, skip_slot);
       const long long r = p - (long long)prefix[t] * nkv;
       const int kvh = (int)(r / sp.pages), page = (int)(r % sp.pages);
       return page_table[(size_t)sp.slot * table_width + (sp.first_page + page) % table_width] * nkv + kvh;
@@ -204,7 +209,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     for (int i = threadIdx.x; i <= ntok; i += CW * 32) prefix_out[i] = prefix[i];
   while (p < p1) {
     // ---- the segment: (token t, kv head kvh), pages [a, b) of the token's span
-    const TokenSpan sp = token_span(t, tok_pos, tok_seq, seq_slot, window);
+    const TokenSpan sp = token_span(t, tok_pos, tok_seq, seq_slot, window, skip_slot);
     const long long r = p - (long long)prefix[t] * nkv;
     const int kvh = (int)(r / sp.pages), a = (int)(r % sp.pages);
     const int b = (int)min((long long)sp.pages, a + (p1 - p));
@@ -347,7 +352,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
     // ---- on to the next segment
     p += b - a;
     ++seg;
-    if (b == sp.pages && kvh + 1 == nkv) ++t;
+    if (p < p1) t = token_of(prefix, ntok, nkv, p);   // the next token that has pages
   }
 }
 
@@ -359,8 +364,9 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
 constexpr int MAX_CTAS = 1024, MERGE_ROUND = 64, MERGE_EPT = 4, MAX_REP = 16, MERGE_COUNT_ITSELF = 256;
 __global__ void __launch_bounds__(1024)
 attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_stride, const float* __restrict__ part,
-                                     const int* __restrict__ prefix, const int* __restrict__ tok_pos, int window,
-                                     int ntok, int nkv, int nh, int G) {
+                                     const int* __restrict__ prefix, const int* __restrict__ tok_pos,
+                                     const int* __restrict__ tok_seq, const int* __restrict__ seq_slot, int window,
+                                     int skip_slot, int ntok, int nkv, int nh, int G) {
   __shared__ int slot_of[MERGE_ROUND];   // scratch slot of a part; -1: that CTA had no pages at all
   __shared__ float fac[MERGE_ROUND][MAX_REP], sum[MERGE_ROUND][MAX_REP];
   __shared__ float run_m[MAX_REP], run_l[MAX_REP], scale[MAX_REP];
@@ -377,10 +383,7 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
       for (int base = 0; base < ntok; base += 32) {
         const int i = base + lane;
         int v = 0;
-        if (i < ntok) {
-          const int hi = tok_pos[i] + 1, lo = window > 0 ? max(0, hi - window) : 0;
-          v = (hi - 1) / KEYS - lo / KEYS + 1;
-        }
+        if (i < ntok) v = token_span(i, tok_pos, tok_seq, seq_slot, window, skip_slot).pages;
         int incl = v;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -424,6 +427,11 @@ attention_decode_stream_merge_kernel(bf16* __restrict__ out, long long out_strid
   }
   if (n > 1) slots_of_round(0, min(MERGE_ROUND, n));
   if (early) pdl_wait_prior();   // every CTA waits, also one with nothing to add: the kernel after this one relies on it
+  if (pages == 0) {   // a row of no sequence: zeros, so that what follows stays finite
+    for (int i = tid; i < rep * HD; i += nthr)
+      out[(size_t)t * out_stride + (size_t)(kvh * rep + i / HD) * HD + i % HD] = __float2bfloat16_rn(0.f);
+    return;
+  }
   if (n == 1) return;
   float acc[MERGE_EPT];
 #pragma unroll
@@ -512,7 +520,9 @@ static size_t stream_smem(int ntok, int rep) {
 
 // q, out: [ntok, nh * HD] bfloat16 (q rows 4-byte aligned).  kcache: [pages, nkv, 64, HD],
 // vcache: [pages, nkv, HD, 64], 16-byte aligned.  ctas: CTAs to launch (0: two per SM when they
-// fit, else one).  scratch: float32, at least gb_attention_decode_stream_scratch(...) values.
+// fit, else one).  skip_slot: tokens of this slot belong to no sequence: nothing is read for them
+// and their rows of out are zero (-1: none).  scratch: float32, at least
+// gb_attention_decode_stream_scratch(...) values.
 GB_EXPORT long long gb_attention_decode_stream_scratch(int ntok, int nh, int nkv, int ctas) {
   if (nkv <= 0) return 0;
   return (long long)ctas * 2 * (nh / nkv) * (HD + 2) + ntok + 1;
@@ -522,7 +532,7 @@ GB_EXPORT int gb_attention_decode_stream(const void* q, long long q_stride, void
                                          const void* kcache, const void* vcache, long long pages,
                                          const int* page_table, int table_width, int page_size, int nkv, int hd,
                                          const int* tok_pos, const int* tok_seq, const int* seq_slot, int ntok, int nh,
-                                         int window, int ctas, float* scratch, cudaStream_t stream) {
+                                         int window, int skip_slot, int ctas, float* scratch, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (hd != HD || page_size != KEYS || nkv <= 0 || nh % nkv || nh / nkv > 16 || ntok > MAX_TOKENS || ctas <= 0 || ctas > MAX_CTAS)
     return GB_ERR_SIZE;
@@ -545,15 +555,15 @@ GB_EXPORT int gb_attention_decode_stream(const void* q, long long q_stride, void
 #ifdef GB_STREAM_PLAIN_LAUNCH
   attention_decode_stream_kernel<<<ctas, THREADS, smem, stream>>>(
       mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq,
-      seq_slot, ntok, nh, window, part, prefix);
+      seq_slot, ntok, nh, window, skip_slot, part, prefix);
 #else
   gb_launch(attention_decode_stream_kernel, dim3(ctas), dim3(THREADS), smem, stream, mk, mv, (const bf16*)q, q_stride,
-            (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq, seq_slot, ntok, nh, window, part,
-            prefix);
+            (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq, seq_slot, ntok, nh, window, skip_slot,
+            part, prefix);
 #endif
   const int merge_threads = rep * HD >= 1024 ? 1024 : (rep * HD + 31) / 32 * 32;
   gb_launch(attention_decode_stream_merge_kernel, dim3(ntok * nkv), dim3(merge_threads), 0, stream, (bf16*)out, out_stride,
-            (const float*)part, (const int*)prefix, tok_pos, window, ntok, nkv, nh, ctas);
+            (const float*)part, (const int*)prefix, tok_pos, tok_seq, seq_slot, window, skip_slot, ntok, nkv, nh, ctas);
   return gb_launch_status();
 }
 

@@ -276,7 +276,7 @@ class _DecodeGraph:
             compute=model.compute, act_dtype=model.act_dtype, device=dev, n_tokens=bp, n_seqs=bp,
             tok_pos=self.d_pos, tok_seq=self.d_seq, seq_slot=self.d_slot, seq_start=self.d_start, seq_len=self.d_len,
             cu_seqlens=self.d_cu, is_decode=True, max_new=1, max_total=len_bucket, cache=runner.cache,
-            page_size=runner.cache.page_size)
+            page_size=runner.cache.page_size, pad_slot=pad_slot)
         # once eagerly (loads the kernels, warms the allocator), then captured
         build.set_pdl(True)
         try:

@@ -456,11 +456,12 @@ def attention_decode_stream_usable(ntok: int, nh: int, nkv: int, hd: int, page_s
 
 
 def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot,
-                            window=None, ctas=None):
+                            window=None, ctas=None, skip_slot=None):
     """bfloat16 attention of single positions with the cache streamed through shared memory by
     TMA: the pages that the step reads are dealt evenly to the CTAs as one flat list, whatever the
     lengths of the sequences; parts of a (token, kv head) that fall to different CTAs are added
-    in key order by a second kernel."""
+    in key order by a second kernel.  Tokens of ``skip_slot`` (rows that pad a captured step) read
+    nothing and get zeros."""
     _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot)
     nkv, hd = kcache.shape[1], kcache.shape[3]
     ntok = q.shape[0]
@@ -473,7 +474,7 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
                           f"(at most {STREAM_DECODE_MAX_TOKENS}) not supported")
     defines = (("GB_HEAD_DIM", hd),)
     sig = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int,
-           c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+           c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     f = _fn("attention_decode_stream", "gb_attention_decode_stream", sig, defines=defines)
     if ctas is None:
         ctas = _SM_COUNT   # measured at 8,192 keys, batch 1 / 8 / 64: 17 / 54 / 323 us; two per SM: 24 / 58 / 329
@@ -486,7 +487,8 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
                                                                        device=q.device)
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
              kcache.shape[0], page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(),
-             tok_seq.data_ptr(), seq_slot.data_ptr(), ntok, nh, window or 0, ctas, scratch.data_ptr(), _stream()),
+             tok_seq.data_ptr(), seq_slot.data_ptr(), ntok, nh, window or 0, -1 if skip_slot is None else skip_slot,
+             ctas, scratch.data_ptr(), _stream()),
            "attention_decode_stream")
     count_launches(1)   # the merge kernel
 
@@ -614,7 +616,7 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
         nkv = kcache.shape[1]
         if attention_decode_stream_usable(ctx.n_tokens, nh, nkv, kcache.shape[3], page_size):
             attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq,
-                                    ctx.seq_slot, window)
+                                    ctx.seq_slot, window, skip_slot=ctx.pad_slot)
             return
         shares = decode_shares(ctx.n_tokens, nh, nkv, ctx.max_total if window is None else min(ctx.max_total, window))
         attention_decode(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,

@@ -57,6 +57,7 @@ class StepContext:
     cache: object                      # the SequenceCache
     page_size: int
     extras: dict = dataclasses.field(default_factory=dict)
+    pad_slot: Optional[int] = None     # slot of rows that belong to no sequence (a padded captured step)
 
     def empty(self, shape, dtype=None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.act_dtype, device=self.device)

@@ -264,6 +264,20 @@ def test_attention_decode_stream_against_plain(k, hd, nh, nkv, window, ring):
         k.attention_decode_stream(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, ctas=ctas)
         err = (out.float() - ref).abs().max().item()
         assert err <= 2 ** -7 * max(1.0, ref.abs().max().item()), f"ctas={ctas}: {err}"
+    # rows that belong to no sequence (the slot that pads a captured step), first, in the middle and
+    # last: nothing is read for them, their rows are zero, the others as before
+    skip = 1000
+    for padded in ([0], [2, 3], [5, 6], [0, 1, 2, 3, 4, 5]):
+        slots = seq_slot.clone()
+        slots[padded] = skip
+        for ctas in (None, 3):
+            k._decode_stream_scratch[q.device.index].fill_(float("nan"))
+            out = torch.full_like(q, 7.0)
+            k.attention_decode_stream(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, slots, window, ctas=ctas, skip_slot=skip)
+            want = ref.clone()
+            want[padded] = 0
+            err = (out.float() - want).abs().max().item()
+            assert err <= 2 ** -7 * max(1.0, ref.abs().max().item()), f"padded={padded} ctas={ctas}: {err}"
     assert k.attention_decode_stream_status() == 0
     with pytest.raises(k.KernelError):
         k.attention_decode_stream(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, ctas=5000)
