@@ -115,14 +115,6 @@ __device__ __forceinline__ void st_peer_f32(float* local, uint32_t rank, float v
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-__device__ __forceinline__ float ld_peer_f32(const float* local, uint32_t rank) {
-  uint32_t addr;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
-  return v;
-}
-
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
 // groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
