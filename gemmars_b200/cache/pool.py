@@ -219,8 +219,10 @@ class CacheBinding:
 class SequenceCache:
     """All groups of a model, the slots, and each sequence's length.
 
-    ``needs``: for each schedule entry that keeps a cache, ``(entry index, KVNeed | StateNeed)``.
-    Entries with equal needs share a group.
+    ``needs``: for each schedule entry that keeps a cache, ``(entry index, needs)``, ``needs``
+    being one ``KVNeed | StateNeed`` or a list of them (a layer may keep keys and a state, or two
+    states of different shapes).  Equal needs share a group, whichever entry they come from.
+    ``bindings[entry]`` lists, in the order of the entry's needs, where each one lives.
     """
 
     def __init__(self, needs: Sequence[Tuple[int, object]], max_tokens: int, n_slots: int, max_positions: int,
@@ -238,21 +240,24 @@ class SequenceCache:
         kv_keys: List[KVNeed] = []
         st_keys: List[StateNeed] = []
         members: Dict[Tuple[str, int], List[int]] = {}
-        self.bindings: Dict[int, CacheBinding] = {}
-        for entry, need in needs:
-            if isinstance(need, KVNeed):
-                if need not in kv_keys:
-                    kv_keys.append(need)
-                g, kind = kv_keys.index(need), "kv"
-            elif isinstance(need, StateNeed):
-                if need not in st_keys:
-                    st_keys.append(need)
-                g, kind = st_keys.index(need), "state"
-            else:
-                raise TypeError(f"schedule entry {entry}: unknown cache need {need!r}")
-            lst = members.setdefault((kind, g), [])
-            self.bindings[entry] = CacheBinding(kind, g, len(lst))
-            lst.append(entry)
+        self.bindings: Dict[int, List[CacheBinding]] = {}
+        for entry, entry_needs in needs:
+            if isinstance(entry_needs, (KVNeed, StateNeed)):
+                entry_needs = [entry_needs]
+            for need in entry_needs:
+                if isinstance(need, KVNeed):
+                    if need not in kv_keys:
+                        kv_keys.append(need)
+                    g, kind = kv_keys.index(need), "kv"
+                elif isinstance(need, StateNeed):
+                    if need not in st_keys:
+                        st_keys.append(need)
+                    g, kind = st_keys.index(need), "state"
+                else:
+                    raise TypeError(f"schedule entry {entry}: unknown cache need {need!r}")
+                lst = members.setdefault((kind, g), [])
+                self.bindings.setdefault(entry, []).append(CacheBinding(kind, g, len(lst)))
+                lst.append(entry)
         self.kv_groups = [KVGroup(n, len(members[("kv", i)]), self.n_slots, self.n_pages, max_seq_pages,
                                   max_step_tokens, dtype, device, page_size) for i, n in enumerate(kv_keys)]
         self.state_groups = [StateGroup(n, len(members[("state", i)]), self.n_slots, device)
@@ -304,17 +309,41 @@ class SequenceCache:
         for g in self.kv_groups:
             g.sync()
 
-    def kv(self, entry: int):
-        b = self.bindings[entry]
-        assert b.kind == "kv"
-        g = self.kv_groups[b.group]
-        k, v = g.layer(b.index)
-        return g, k, v
+    def rollback(self, slot: int, old_len: int) -> bool:
+        """After a step that failed: takes back the positions from ``old_len`` on that were
+        reserved for it, so that the slot's length again names only positions that were written
+        by steps that succeeded.  Returns whether the slot then holds exactly what it held before
+        the step: true when every group keeps all keys (their pages beyond ``old_len`` are given
+        back); false when a window's ring may have been written over or a state may have
+        advanced, which cannot be undone: such a slot can only be closed."""
+        if slot not in self.lengths or old_len >= self.lengths[slot]:
+            return True
+        for g in self.kv_groups:
+            if g.need.window is None:
+                g.truncate(slot, old_len)
+        self.lengths[slot] = old_len
+        return not self.state_groups and all(g.need.window is None for g in self.kv_groups)
 
-    def state(self, entry: int) -> torch.Tensor:
-        b = self.bindings[entry]
-        assert b.kind == "state"
-        return self.state_groups[b.group].layer(b.index)
+    def views(self, entry: int) -> list:
+        """The storage of every need of ``entry``, in the order of its needs: ``(KVGroup, k, v)``
+        for keys and values, the state tensor ``[slots + 1, *shape]`` for a state."""
+        out = []
+        for b in self.bindings.get(entry, []):
+            if b.kind == "kv":
+                g = self.kv_groups[b.group]
+                out.append((g,) + tuple(g.layer(b.index)))
+            else:
+                out.append(self.state_groups[b.group].layer(b.index))
+        return out
+
+    def kv(self, entry: int, which: int = 0):
+        """(group, k, v) of the ``which``-th need of ``entry``, which must be a KVNeed."""
+        assert self.bindings[entry][which].kind == "kv"
+        return self.views(entry)[which]
+
+    def state(self, entry: int, which: int = 0) -> torch.Tensor:
+        assert self.bindings[entry][which].kind == "state"
+        return self.views(entry)[which]
 
     def pages_held(self) -> int:
         return sum(g.pages.held_count for g in self.kv_groups)

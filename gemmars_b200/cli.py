@@ -96,7 +96,6 @@ def main(argv=None) -> int:
         opts.set("profile", "true")
     eng = Engine.load(args.model, opts)
     if args.profile:
-        eng._profile_from = eng.runner.steps_run
         eng.profile_start()
     for k, v in (("max_tokens", args.max_tokens), ("temperature", args.temp), ("top_k", args.top_k),
                  ("top_p", args.top_p), ("seed", args.seed)):

@@ -15,6 +15,7 @@ import os
 from typing import Any, Optional
 
 REQUIRED = object()
+_NULLABLE = ("opt_int", "str_list", "opt_dict")
 
 
 class ConfigError(ValueError):
@@ -24,7 +25,7 @@ class ConfigError(ValueError):
 def key(kind, default=REQUIRED, *, doc=""):
     """A dataclass field read from config.json under the field's own name.
 
-    ``kind`` is int, float, bool, str, "int_list", "str_list" or "opt_int".
+    ``kind`` is int, float, bool, str, "int_list", "str_list", "opt_int" or "opt_dict".
     """
     md = {"kind": kind, "required": default is REQUIRED, "doc": doc}
     if default is REQUIRED:
@@ -69,6 +70,10 @@ def _coerce(name, kind, value, errors):
         if isinstance(value, list) and all(isinstance(v, str) for v in value):
             return list(value)
         return bad("a list of strings or null")
+    if kind == "opt_dict":
+        if value is None or isinstance(value, dict):
+            return value
+        return bad("an object or null")
     raise TypeError(f"unknown key kind {kind!r}")
 
 
@@ -93,10 +98,10 @@ class ModelConfig:
                     errors.append(f"{f.name}: missing")
                 continue
             value = text[f.name] if f.name in text else raw[f.name]
-            if value is None and not md["required"] and md["kind"] not in ("opt_int", "str_list"):
+            if value is None and not md["required"] and md["kind"] not in _NULLABLE:
                 continue  # an explicit null means "default"
             got = _coerce(f.name, md["kind"], value, errors)
-            if got is not None or md["kind"] in ("opt_int", "str_list"):
+            if got is not None or md["kind"] in _NULLABLE:
                 values[f.name] = got
         if errors:
             raise ConfigError("config.json: " + "; ".join(errors))

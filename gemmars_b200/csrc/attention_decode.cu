@@ -24,9 +24,6 @@
 #ifndef GB_HEAD_DIM
 #define GB_HEAD_DIM 128
 #endif
-#ifndef GB_DECODE_MIN_CTAS
-#define GB_DECODE_MIN_CTAS 1      // CTAs the compiler must fit on an SM (caps registers per thread)
-#endif
 
 namespace {
 
@@ -39,7 +36,7 @@ static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head size must be a multip
 // grid (shares, kv heads * head chunks, tokens); block WARPS * 32.
 // part_o: [tokens, nh, shares, HD]; part_ml: [tokens, nh, shares, 2] (m in log2 units, l).
 template <bool UPPER>   // UPPER: more than 8 query heads per chunk (rows 8..15 of the MMA in use)
-__global__ void __launch_bounds__(WARPS * 32, GB_DECODE_MIN_CTAS)
+__global__ void __launch_bounds__(WARPS * 32, 1)
 attention_decode_kernel(const bf16* __restrict__ q, long long q_stride, bf16* __restrict__ out, long long out_stride,
                         const bf16* __restrict__ kcache, const bf16* __restrict__ vcache, PagedKV kv,
                         const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
@@ -321,12 +318,20 @@ GB_EXPORT int gb_attention_decode_static(const void* q, long long q_stride, void
                                          const int* tok_seq, const int* seq_slot, int ntok, int nh, int window,
                                          int shares, cudaStream_t stream) {
   if (ntok <= 0) return 0;
-  if (shares < 1 || nh <= 0) return GB_ERR_SIZE;
-  const unsigned long long need = (unsigned long long)ntok * nh * shares * (HD + 2);
-  if (shares > 1 && need > GB_ATTENTION_DECODE_STATIC_FLOATS) return GB_ERR_STATIC_SCRATCH;
-  int error = 0;
-  float* scratch = static_scratch_address(&error);
-  if (!scratch) return error;
+  // sizes first, each against its own bound, so that the product below cannot wrap
+  if (hd != HD || nkv <= 0 || nh <= 0 || nh % nkv || shares < 1 || shares > 65535) return GB_ERR_SIZE;
+  float* scratch = nullptr;
+  if (shares > 1) {
+    const unsigned long long per_share = (unsigned long long)(HD + 2) * (unsigned)shares;   // < 2^25
+    const unsigned long long rows_allowed = GB_ATTENTION_DECODE_STATIC_FLOATS / per_share;
+    if ((unsigned long long)ntok > rows_allowed || (unsigned long long)ntok * (unsigned)nh > rows_allowed)
+      return GB_ERR_STATIC_SCRATCH;
+    // one share writes its result itself and needs no scratch: the array's address is looked up
+    // only when it is used
+    int error = 0;
+    scratch = static_scratch_address(&error);
+    if (!scratch) return error;
+  }
   return gb_attention_decode(q, q_stride, out, out_stride, kcache, vcache, page_table, table_width, page_size, nkv, hd,
                              tok_pos, tok_seq, seq_slot, ntok, nh, window, shares, scratch, stream);
 }

@@ -9,9 +9,12 @@
 // when the keys are split over several CTAs ("shares" > 1).
 //
 // Here that scratch is a fixed array in the library's own device data segment,
-// GB_ATTENTION_DECODE_STATIC_FLOATS float32 values (4 MiB).  Every GPU on which this library is
-// loaded holds those 4 MiB from the moment the library's module is loaded on it until the
-// process ends, whether or not this function is ever called.
+// GB_ATTENTION_DECODE_STATIC_FLOATS float32 values (4 MiB).  The array belongs to one built
+// library: attention_decode is built once per head size (and once more for the variant whose
+// kernels start under their predecessor), and each of those builds that a process loads carries
+// an array of its own.  Every GPU on which such a build is loaded holds its 4 MiB from the
+// moment the build's module is loaded there until the process ends, whether or not this
+// function is ever called.
 //
 // Arguments and result are those of gb_attention_decode (attention_decode.cu) without the
 // scratch pointer.  The library is built for one head size; `hd` must be that size.
@@ -20,8 +23,10 @@
 //    shares > 1, else GB_ERR_STATIC_SCRATCH (-5) is returned and nothing is launched.  With
 //    hd = 128 that is, for instance, 64 tokens x 32 heads x 3 shares, or 8 tokens x 32 heads x 31.
 //  * It calls no cudaMalloc, cudaFree or other allocating routine, and launches on `stream`.
-//  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-//    that device current) and remembers it; make that first call before any stream capture begins.
+//  * The first call with shares > 1 on a device looks up the array's device address
+//    (cudaGetSymbolAddress, with that device current) and remembers it; make that first call
+//    before any stream capture begins.  A call with shares == 1 needs no scratch and looks
+//    nothing up.
 //  * All calls on a device share the one array and it keeps what the last call left.  Nothing in
 //    it needs clearing between calls, but two calls whose kernels may run at the same time
 //    (different streams without an ordering between them) race on it: order them.
@@ -32,8 +37,14 @@
 #define GB_ATTENTION_DECODE_STATIC_FLOATS (1u << 20)
 #define GB_ERR_STATIC_SCRATCH (-5)
 
-extern "C" int gb_attention_decode_static(const void* q, long long q_stride, void* out, long long out_stride,
+#ifdef __cplusplus
+extern "C" {
+#endif
+int gb_attention_decode_static(const void* q, long long q_stride, void* out, long long out_stride,
                                           const void* kcache, const void* vcache, const int* page_table,
                                           int table_width, int page_size, int nkv, int hd, const int* tok_pos,
                                           const int* tok_seq, const int* seq_slot, int ntok, int nh, int window,
                                           int shares, cudaStream_t stream);
+#ifdef __cplusplus
+}
+#endif

@@ -552,15 +552,9 @@ GB_EXPORT int gb_attention_decode_stream(const void* q, long long q_stride, void
   }
   float* part = scratch;
   int* prefix = (int*)(scratch + (size_t)ctas * 2 * rep * (HD + 2));
-#ifdef GB_STREAM_PLAIN_LAUNCH
-  attention_decode_stream_kernel<<<ctas, THREADS, smem, stream>>>(
-      mk, mv, (const bf16*)q, q_stride, (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq,
-      seq_slot, ntok, nh, window, skip_slot, part, prefix);
-#else
   gb_launch(attention_decode_stream_kernel, dim3(ctas), dim3(THREADS), smem, stream, mk, mv, (const bf16*)q, q_stride,
             (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq, seq_slot, ntok, nh, window, skip_slot,
             part, prefix);
-#endif
   const int merge_threads = rep * HD >= 1024 ? 1024 : (rep * HD + 31) / 32 * 32;
   gb_launch(attention_decode_stream_merge_kernel, dim3(ntok * nkv), dim3(merge_threads), 0, stream, (bf16*)out, out_stride,
             (const float*)part, (const int*)prefix, tok_pos, tok_seq, seq_slot, window, skip_slot, ntok, nkv, nh, ctas);

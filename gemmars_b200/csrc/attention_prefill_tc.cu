@@ -74,12 +74,6 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
-#ifdef GB_TRACE
-__device__ long long g_attn_trace[64 * 16];
-#define ATRACE(j, slot) do { if (traced && (j) < 64) g_attn_trace[(j) * 16 + (slot)] = clock64(); } while (0)
-#else
-#define ATRACE(j, slot)
-#endif
 
 __device__ __forceinline__ float ex2(float x) {   // 2^x, one instruction; 2^-inf = 0
   float y;
@@ -139,9 +133,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int pos_last = start + first + rows_valid - 1;
   const int lo_first = window > 0 ? max(0, start + first + 1 - window) : 0;
   const int kt_begin = lo_first / KEYS, n_tiles = pos_last / KEYS + 1 - kt_begin;
-#ifdef GB_TRACE
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 1 && (threadIdx.x & 31) == 0;   // one long tile of head 0
-#endif
 
   if (threadIdx.x == 0) {
     if (smem_u32(smem) & 1023u) {   // the swizzled tiles need 1024-byte alignment
@@ -192,7 +183,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         bool moved = false;
         if (jk < n_tiles && (jk < 2 || mbar_try_wait(&k_empty[jk & 1], ((jk >> 1) - 1) & 1))) {
           const int sidx = jk & 1;
-          ATRACE(jk, 0);   // producer: keys' stage free, about to load page jk
           const int page = page_table[(size_t)slot * table_width + (kt_begin + jk) % table_width];
           const int row = page * nkv + kvh;
           mbar_expect_tx(&k_full[sidx], K_BYTES);
@@ -232,7 +222,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (js < n_tiles && mbar_try_wait(&k_full[js & 1], (js >> 1) & 1) &&
             (js < 2 || mbar_try_wait(&s_empty[js & 1], ((js >> 1) - 1) & 1))) {
           const int sidx = js & 1;
-          ATRACE(js, 2);   // MMA: keys here and S buffer free, issuing S
           tc_fence_after();
           const uint32_t d = tmem + (sidx ? S_COL1 : S_COL0);
 #pragma unroll
@@ -248,7 +237,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           moved = true;
         }
         if (jp < js && mbar_try_wait(p_full, jp & 1) && mbar_try_wait(&v_full[jp & 1], (jp >> 1) & 1)) {
-          ATRACE(jp, 3);   // MMA: P and the values are there, issuing P V
           tc_fence_after();
           const uint64_t pd = smem_desc(smem_u32(p_smem));
           const uint64_t vd = smem_desc(smem_u32(v_smem + (jp & 1) * V_BYTES));
@@ -280,10 +268,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     bool ok = !*abort;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int sb = j & 1;
-      if (warp == 0) ATRACE(j, 4);   // softmax warp 0: starts to wait for S_j
       ok = __all_sync(0xffffffffu, wait_or_abort(&s_full[sb], (j >> 1) & 1, abort, 6));
       if (!ok) break;
-      if (warp == 0) ATRACE(j, 5);   // softmax warp 0: S_j seen
       tc_fence_after();
       uint32_t sv[64];
       tc_ld32(lane_addr + (sb ? S_COL1 : S_COL0), sv);
@@ -334,13 +320,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         pk[c] = pack2(a, bq);
       }
       l = l * alpha + (sum0 + sum1);
-      if (warp == 0) ATRACE(j, 6);   // softmax warp 0: exponentials done
       if (j > 0) {
         // O of the pages before is complete; bring it to the new maximum where that moved
         ok = __all_sync(0xffffffffu, wait_or_abort(o_done, (j - 1) & 1, abort, 6));
         if (!ok) break;
         tc_fence_after();
-        if (warp == 0) ATRACE(j, 7);   // softmax warp 0: PV_{j-1} seen done
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
           for (int c = 0; c < HD; c += 32) {
@@ -363,8 +347,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
-      if (warp == 0) ATRACE(j, 8);   // softmax warp 0: P_j written
-      if (warp == 3) ATRACE(j, 9);   // softmax warp 3: P_j written
     }
     if (ok) ok = __all_sync(0xffffffffu, wait_or_abort(o_done, (n_tiles - 1) & 1, abort, 6));
     if (ok) {
@@ -430,11 +412,6 @@ GB_EXPORT int gb_attention_prefill_tc(const void* q, long long q_stride, void* o
 }
 
 // 0, or the code of the first bounded wait that ran out (synchronizes the device).
-#ifdef GB_TRACE
-GB_EXPORT int gb_attention_prefill_tc_trace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(long long) * n);
-}
-#endif
 
 GB_EXPORT int gb_attention_prefill_tc_status(int reset) {
   int v = -1;

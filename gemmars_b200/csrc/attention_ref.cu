@@ -23,7 +23,8 @@ __global__ void __launch_bounds__(CHUNK) attention_ref_kernel(
   float* qs = smem;                    // [hd]
   float* p = qs + hd;                  // [CHUNK]
   float* scratch = p + CHUNK;          // [33]
-  size_t* rows = (size_t*)(scratch + 34);  // [CHUNK]
+  // [CHUNK]; 8-byte aligned whatever the head size (the launcher adds the 8 bytes this may skip)
+  size_t* rows = (size_t*)(((uintptr_t)(scratch + 34) + 7) & ~(uintptr_t)7);
   const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
   const int g = h / (nh / kv.num_kv_heads);
   const int pos = tok_pos[t];

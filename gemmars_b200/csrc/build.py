@@ -74,8 +74,6 @@ def library_path(unit: str, defines: Sequence[Tuple[str, object]] = ()) -> Tuple
     if not os.path.exists(src):
         raise KernelBuildError(f"no CUDA source {src}")
     flags = ARCH_FLAGS + BASE_FLAGS + [f"-D{k}={v}" for k, v in defines]
-    # further defines for every unit (experiments), e.g. GEMMARS_B200_DEFINES="GB_DECODE_MIN_CTAS=2"
-    flags += [f"-D{d.strip()}" for d in os.environ.get("GEMMARS_B200_DEFINES", "").split(",") if d.strip()]
     h = hashlib.sha256()
     with open(src, "rb") as f:
         h.update(f.read())

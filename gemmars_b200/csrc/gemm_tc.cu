@@ -63,25 +63,6 @@ enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3
 
 __device__ int g_status;   // first failure of any launch; 0 when all waits completed
 
-// -DGB_TRACE: thread 0 of every CTA of gemm_tc_kernel stamps the global timer at eight points
-// (entry, set-up done, first and last operands, accumulator done, cluster barrier, stored, exit);
-// gb_gemm_tc_trace copies the stamps of the last launch out.  For finding where a launch's time goes.
-#ifdef GB_TRACE
-__device__ unsigned long long g_trace[4096 * 8];
-__device__ __forceinline__ void trace(int slot) {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
-  if (cta < 4096) g_trace[cta * 8 + slot] = t;
-}
-#ifdef GB_TRACE_MODE   // only the kernels of one epilogue mode record (the last such launch stays)
-#define TRACE(slot) do { if (MODE == GB_TRACE_MODE) trace(slot); } while (0)
-#else
-#define TRACE(slot) trace(slot)
-#endif
-#else
-#define TRACE(slot)
-#endif
 
 
 // silu(g) * u with the hardware's exp2 and reciprocal (two special-function instructions): the
@@ -298,7 +279,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb_count = kb_end - kb_begin;
 
   if (threadIdx.x == 0) {
-    TRACE(0);
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -314,7 +294,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  if (threadIdx.x == 0) TRACE(1);
 
   if (warp == 4) {
     // ---------------- TMA producer
@@ -331,8 +310,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (DUAL) tma_load_2d(a + W_BYTES, &map_w, (kb_begin + i) * BK, N + n0, &full_bar[i]);   // the up rows
       }
       pdl_wait_prior();
-      for (int i = 0; i < pre; ++i)
+      for (int i = 0; i < pre; ++i) {
+#ifdef GB_TEST_WITHHOLD_LOAD
+        // Test build only: the tokens of the last block are never asked for, so its stage never
+        // fills and the MMA thread's bounded wait runs out.  It shows that a wait which gives up
+        // sets the status word and that the CTA still leaves through the common exit.
+        if (i == kb_count - 1) continue;
+#endif
         tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full_bar[i]);
+      }
       for (int i = pre; i < kb_count; ++i) {
         const int s = i % STAGES;
         if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) {
@@ -343,6 +329,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         mbar_expect_tx(&full_bar[s], STAGE_BYTES);
         tma_load_2d(a, &map_w, (kb_begin + i) * BK, n0, &full_bar[s]);
         if (DUAL) tma_load_2d(a + W_BYTES, &map_w, (kb_begin + i) * BK, N + n0, &full_bar[s]);   // the up rows
+#ifdef GB_TEST_WITHHOLD_LOAD
+        if (i == kb_count - 1) continue;
+#endif
         tma_load_2d(a + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full_bar[s]);
       }
       // the last load is on its way: the next kernel may move in and ask for its first weights
@@ -362,8 +351,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           break;
         }
         tc_fence_after();
-        if (i == 0) TRACE(2);
-        if (i == kb_count - 1) TRACE(3);
         const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES), udesc = smem_desc(a + W_BYTES);
 #pragma unroll
@@ -398,7 +385,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       if (!have_acc && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
     }
     tc_fence_after();
-    if (threadIdx.x == 0) TRACE(4);
   }
   if (nsplit > 1) {
     // Every rank sends each token's partial sums to the rank that finishes the token, into that
@@ -442,7 +428,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
     }
     cluster_sync();
-    if (threadIdx.x == 0) TRACE(5);
     if (warp < 4) {
       const int f = warp * 32 + lane, n = n0 + f;
 #pragma unroll 1
@@ -512,12 +497,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     if (by_tma) tile_out.finish(lane);
   }
-  if (threadIdx.x == 0) TRACE(6);
   tc_fence_before();
   __syncthreads();
   __syncwarp();
   if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
-  if (threadIdx.x == 0) TRACE(7);
 }
 
 // ------------------------------------------------------------------ the persistent kernel for prompts
@@ -543,12 +526,6 @@ __device__ __forceinline__ void tile_origin(int t, int tiles_m, int tiles_n, int
   n0 = (r / gm) * tile_features;
 }
 
-#ifdef GB_TRACE
-__device__ long long g_ptrace[256 * 8];
-#define PTRACE(idx, slot) do { if (blockIdx.x == 0 && (idx) < 256) g_ptrace[(idx) * 8 + (slot)] = clock64(); } while (0)
-#else
-#define PTRACE(idx, slot)
-#endif
 
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -621,7 +598,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             break;
           }
           uint8_t* a = smem + s * STAGE_BYTES;
-          PTRACE(it, 0);   // producer: stage free, loading block `it`
           mbar_expect_tx(&full_bar[s], stage_tx);
           if (GATED) {   // map_w is cut into boxes of 64 rows: the gate rows, then the same features' up rows
             // (a request costs the issuing thread about 75 cycles: boxes of 16 rows, which would let a
@@ -658,14 +634,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             break;
           }
           tc_fence_after();
-          PTRACE(it, 1);   // MMA: block `it` has arrived
           const uint32_t a = smem_u32(smem + s * STAGE_BYTES);
           const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             tc_mma(d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
           tc_commit(&empty_bar[s]);
-          PTRACE(it, 2);   // MMA: block `it` issued
         }
         tc_commit(&acc_full[b]);
       }
@@ -694,7 +668,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       }
       if (!have) break;
       tc_fence_after();
-      if (threadIdx.x == 0) PTRACE(i, 3);   // epilogue: tile i complete
       const float bv = (bias && n < N) ? bias[n] : 0.f;
       const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16) + b * ACC_COLS;
 #pragma unroll 1
@@ -737,7 +710,6 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
-      if (threadIdx.x == 0) PTRACE(i, 4);   // epilogue: tile i stored
     }
     if (y_tma) tile_out.finish(lane);
   }
@@ -942,14 +914,6 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
   return GB_ERR_ARG;
 }
 
-#ifdef GB_TRACE
-GB_EXPORT int gb_gemm_tc_persistent_trace(long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_ptrace, sizeof(long long) * n);
-}
-GB_EXPORT int gb_gemm_tc_trace(unsigned long long* host, int n) {
-  return (int)cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n);
-}
-#endif
 
 // The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator).
 // Synchronizes the device; for tests and health checks, not for the step.

@@ -17,7 +17,13 @@
 
 namespace {
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;   // polls of an mbarrier before a wait gives up
+// Polls of an mbarrier before a wait gives up.  A test build may shorten it
+// (-DGB_TEST_WAIT_LIMIT=n) so that a wait which nothing completes runs out in microseconds.
+#ifdef GB_TEST_WAIT_LIMIT
+constexpr uint32_t WAIT_LIMIT = GB_TEST_WAIT_LIMIT;
+#else
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+#endif
 constexpr int TC_BOX_COLS = 64;             // 64 bfloat16 = one 128-byte swizzle row
 
 // ------------------------------------------------------------------ PTX wrappers

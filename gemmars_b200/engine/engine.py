@@ -174,7 +174,9 @@ class Engine:
         def make_sampler(params):
             return BatchSampler([p or self.sampling for p in params], r.device)
 
-        return GenerationLoop(r.open, r.close, step, make_sampler, self.options.max_batch,
+        # a batch is as large as the free slots allow: the conversation of ``send`` holds one
+        return GenerationLoop(r.open, r.close, step, make_sampler,
+                              max(1, min(self.options.max_batch, r.cache.slots.free_count)),
                               r.cache.n_pages - r.cache.pages_held(), r.cache.page_size, self.max_context)
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None,
@@ -211,40 +213,29 @@ class Engine:
     def send(self, tokens: Sequence[int], on_token=None) -> Generated:
         """The next turn of the engine's conversation: appends ``tokens`` to what the cache holds
         and generates a reply; the cache is kept for the turn after (src/engine.rs:981-1064).
-        A last token that was generated but not run is fed first (src/generate.rs:105-128)."""
+        A last token that was generated but not run is fed first (src/generate.rs:105-128).
+        A turn that fails after it began forgets the conversation (``reset``)."""
         r = self.runner
         if self._conv_slot is None:
             self._conv_slot = r.open()
         feed = ([self._unfed] if self._unfed is not None else []) + list(tokens)
-        self._unfed = None
         if not feed:
             raise ValueError("send: no tokens")
-        if r.length(self._conv_slot) + len(feed) > self.max_context:
-            raise ValueError(f"the conversation would exceed the context limit {self.max_context}")
-        sampler = BatchSampler([self.sampling], r.device)
-        t0 = time.perf_counter()
-        logits = r.step([StepItem(self._conv_slot, feed, [len(feed) - 1])])
-        torch.cuda.synchronize(r.device)
-        t1 = time.perf_counter()
-        out, reason, steps = [], LENGTH, 0
-        for _ in range(self.max_new_tokens):
-            tok = sampler.sample(logits, [0])[0]
-            out.append(tok)
-            if tok in self.stop_ids:
-                reason = STOP
-                break
-            if on_token is not None and on_token(out) is False:
-                reason, self._unfed = CANCELLED, tok
-                break
-            if r.length(self._conv_slot) + 1 > self.max_context or len(out) >= self.max_new_tokens:
-                self._unfed = tok
-                break
-            logits = r.step([StepItem(self._conv_slot, [tok], [0])])
-            steps += 1
-        torch.cuda.synchronize(r.device)
-        kernels.check_status()
-        self.stats = Stats(len(feed), len(out), t1 - t0, time.perf_counter() - t1, steps)
-        return Generated(out, reason, len(feed), steps)
+        loop = self._loop()
+        cb = (lambda i, toks: on_token(toks)) if on_token else None
+        req = Request(feed, self.max_new_tokens, tuple(self.stop_ids), self.sampling)
+        try:
+            res = loop.run_in_slot(self._conv_slot, r.length(self._conv_slot), req, cb)
+            kernels.check_status()
+        except ValueError:
+            raise                     # refused before anything ran: the conversation is as it was
+        except BaseException:
+            # a turn that broke off half way leaves a cache that matches no conversation
+            self.reset()
+            raise
+        self._unfed = res.unfed
+        self.stats = Stats(len(feed), loop.decode_tokens, loop.prefill_secs, loop.decode_secs, loop.decode_steps)
+        return res
 
     def reset(self) -> None:
         """Forgets the conversation (src/engine.rs:958)."""
@@ -279,12 +270,13 @@ class Engine:
     def profile_start(self) -> None:
         """Starts the per-kernel timing that ``profile_report`` prints (option ``profile``; decode
         steps then run without CUDA graphs so that every launch can be timed)."""
-        from .. import kernels
+        self._profile_from = self.runner.tokens_run
         kernels.profile_start()
 
     def profile_report(self) -> str:
-        from .. import kernels
-        return kernels.profile_report(max(1, self.runner.steps_run - getattr(self, "_profile_from", 0)))
+        """Time, calls, bytes and bandwidth per category and time per kernel since
+        ``profile_start``, per forward token (src/prof.rs:51-83)."""
+        return kernels.profile_report(max(1, self.runner.tokens_run - getattr(self, "_profile_from", 0)))
 
     def stats_dict(self) -> dict:
         return dataclasses.asdict(self.stats)

@@ -37,6 +37,9 @@ class Generated:
     reason: str                       # "stop", "length" or "cancelled"
     prompt_tokens: int
     forwards: int = 0                 # decode steps this sequence took part in
+    #: the last generated token when it was not run and is no stop token: a later turn of the
+    #: same sequence must feed it first (src/generate.rs:122-127)
+    unfed: Optional[int] = None
 
 
 def tokens_held(prompt_len: int, max_tokens: int, max_context: Optional[int]) -> int:
@@ -96,24 +99,45 @@ class GenerationLoop:
             self._run_batch(requests, batch, results, on_token)
         return results
 
-    def _run_batch(self, requests, batch, results, on_token):
+    def run_in_slot(self, slot: int, held: int, request: Request,
+                    on_token: Optional[Callable[[int, List[int]], bool]] = None) -> Generated:
+        """One more turn of a sequence that lives on in ``slot``, which already holds ``held``
+        positions: ``request.prompt`` is what the turn brings.  The slot stays open afterwards,
+        whatever happens; the same decisions as for a batch apply."""
+        if len(request.prompt) == 0:
+            raise ValueError("the turn brings no token")
+        if self.max_context and held + len(request.prompt) > self.max_context:
+            raise ValueError(f"the conversation would exceed the context limit {self.max_context}")
+        results: List[Optional[Generated]] = [None]
+        self._run_batch([request], [0], results, on_token, kept={0: (slot, held)})
+        return results[0]
+
+    def _run_batch(self, requests, batch, results, on_token, kept=None):
+        """``kept``: {request index: (slot, positions it holds)} for sequences whose slot is the
+        caller's: it is neither opened nor closed here."""
+        kept = kept or {}
         sampler = self.make_sampler([requests[i].sampling for i in batch])
         slots = {}
         try:
             for i in batch:
-                slots[i] = self.open_slot()
+                slots[i] = kept[i][0] if i in kept else self.open_slot()
             out = {i: [] for i in batch}
             forwards = {i: 0 for i in batch}
-            held = {i: len(requests[i].prompt) for i in batch}    # positions in the cache
+            # positions in the cache
+            held = {i: (kept[i][1] if i in kept else 0) + len(requests[i].prompt) for i in batch}
             live = [i for i in batch]
+            fin = (requests, out, forwards, results, slots, live, kept)
             # requests that may generate nothing still get a result
             for i in list(live):
-                if requests[i].max_tokens <= 0:
-                    self._finish(i, LENGTH, requests, out, forwards, results, slots, live)
+                if requests[i].max_tokens <= 0 and i not in kept:
+                    self._finish(i, LENGTH, *fin)
             t_mark, first = time.perf_counter(), True
             if live:
                 logits = self.step([(slots[i], list(requests[i].prompt)) for i in live])
                 self.prefill_steps += 1
+            for i in list(live):
+                if requests[i].max_tokens <= 0:     # a kept sequence: its tokens are run, nothing is drawn
+                    self._finish(i, LENGTH, *fin)
             while live:
                 toks = sampler.sample(logits, [batch.index(i) for i in live])
                 now = time.perf_counter()
@@ -128,13 +152,13 @@ class GenerationLoop:
                     r = requests[i]
                     out[i].append(int(tok))
                     if int(tok) in r.stop_ids:
-                        self._finish(i, STOP, requests, out, forwards, results, slots, live)
+                        self._finish(i, STOP, *fin)
                     elif on_token is not None and on_token(i, out[i]) is False:
-                        self._finish(i, CANCELLED, requests, out, forwards, results, slots, live)
+                        self._finish(i, CANCELLED, *fin)
                     elif len(out[i]) >= r.max_tokens:
-                        self._finish(i, LENGTH, requests, out, forwards, results, slots, live)
+                        self._finish(i, LENGTH, *fin)
                     elif self.max_context and held[i] + 1 > self.max_context:
-                        self._finish(i, LENGTH, requests, out, forwards, results, slots, live)
+                        self._finish(i, LENGTH, *fin)
                     else:
                         nxt.append((i, int(tok)))
                 if not nxt:
@@ -146,10 +170,14 @@ class GenerationLoop:
                     held[i] += 1
         finally:
             for i, s in list(slots.items()):
-                self.close_slot(s)
+                if i not in kept:
+                    self.close_slot(s)
                 del slots[i]
 
-    def _finish(self, i, reason, requests, out, forwards, results, slots, live):
-        results[i] = Generated(out[i], reason, len(requests[i].prompt), forwards[i])
+    def _finish(self, i, reason, requests, out, forwards, results, slots, live, kept):
+        unfed = out[i][-1] if out[i] and reason != STOP else None
+        results[i] = Generated(out[i], reason, len(requests[i].prompt), forwards[i], unfed)
         live.remove(i)
-        self.close_slot(slots.pop(i))
+        slot = slots.pop(i)
+        if i not in kept:
+            self.close_slot(slot)

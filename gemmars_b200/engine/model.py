@@ -13,7 +13,6 @@ from typing import Dict, Optional
 
 import torch
 
-from ..cache.pool import KVNeed, StateNeed
 from ..config.registry import load_config
 from ..csrc import build
 from ..parts import base as parts_base
@@ -37,12 +36,12 @@ class DecoderModel:
 
     # ---- parts and the tensors they want
     def named_parts(self):
-        """(part, its spec) for every part that can hold weights."""
+        """(part, its spec) for every part that can hold weights: the model's own and whatever
+        each block says it built."""
         yield self.embedding, self.plan.embedding
-        for block, ls in zip(self.blocks, self.plan.layers):
-            specs = {"mixer_norm": ls.mixer_norm, "mixer": ls.mixer, "ffn_norm": ls.ffn_norm, "ffn": ls.ffn}
-            for name, part in block.parts().items():
-                yield part, specs[name]
+        for block in self.blocks:
+            for part in block.parts().values():
+                yield part, part.spec
         yield self.final_norm, self.plan.final_norm
         yield self.head, self.plan.head
 
@@ -96,14 +95,14 @@ class DecoderModel:
 
     # ---- cache needs of the schedule
     def cache_needs(self):
-        """[(schedule position, need)] for entries that keep a cache of their own."""
+        """[(schedule position, [needs])] for entries that keep something of their own."""
         needs = []
         for i, e in enumerate(self.plan.schedule):
             if e.cache_of is not None:
                 continue
-            need = self.blocks[e.layer].mixer.cache_need()
-            if need is not None:
-                needs.append((i, need))
+            mine = self.blocks[e.layer].cache_needs()
+            if mine:
+                needs.append((i, list(mine)))
         return needs
 
     # ---- the step
@@ -115,18 +114,9 @@ class DecoderModel:
         for i, e in enumerate(self.plan.schedule):
             owner = i if e.cache_of is None else e.cache_of
             block = self.blocks[e.layer]
-            cache = self._cache_view(ctx, owner)
             ctx.extras["entry"] = i
-            block.forward(ctx, x, cache, writes_cache=e.cache_of is None)
+            block.forward(ctx, x, ctx.cache.views(owner), writes_cache=e.cache_of is None)
         return x
-
-    def _cache_view(self, ctx, owner):
-        binding = ctx.cache.bindings.get(owner)
-        if binding is None:
-            return None
-        if binding.kind == "kv":
-            return ctx.cache.kv(owner)
-        return ctx.cache.state(owner)
 
     def logits(self, ctx: StepContext, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the packed-token rows ``rows`` (int32)."""
@@ -134,15 +124,19 @@ class DecoderModel:
         return self.head.forward(ctx, h)
 
     def weight_bytes(self) -> int:
-        """Bytes of weights a decode step reads (every matrix once; tied tensors once)."""
-        seen, total = set(), 0
-        for part, _ in self.named_parts():
-            for attr in vars(part).values():
-                w = getattr(attr, "weight", None)
-                if isinstance(w, torch.Tensor) and w.data_ptr() not in seen and w.dim() == 2:
-                    seen.add(w.data_ptr())
-                    total += w.numel() * w.element_size()
+        """Bytes of weights a decode step reads: what each part says of itself, every run of the
+        schedule counted (a layer that runs twice is read twice)."""
+        runs = {}
+        for e in self.plan.schedule:
+            runs[e.layer] = runs.get(e.layer, 0) + 1
+        total = self.embedding.weight_bytes() + self.final_norm.weight_bytes() + self.head.weight_bytes()
+        for i, block in enumerate(self.blocks):
+            total += runs.get(i, 0) * sum(part.weight_bytes() for part in block.parts().values())
         return total
+
+    @property
+    def capture_depends_on_length(self) -> bool:
+        return any(part.capture_depends_on_length for part, _ in self.named_parts())
 
 
 def build_model(folder: Optional[str] = None, *, raw_config: Optional[dict] = None,

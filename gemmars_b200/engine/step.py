@@ -79,8 +79,11 @@ class Runner:
         self.use_graphs = use_graphs
         self._graphs = {}
         self._pool = None
+        self._length_matters = model.capture_depends_on_length
+        self._broken = set()      # slots a failed step left in a state that cannot be restored
         self._ring = _PinnedRing(4 * self.max_step_tokens + 8 * self.cache.n_slots + 64) if self.device.type == "cuda" else None
         self.steps_run = 0
+        self.tokens_run = 0
 
     def _graph_pool(self):
         if self._pool is None:
@@ -93,6 +96,7 @@ class Runner:
 
     def close(self, slot: int) -> None:
         self.cache.close(slot)
+        self._broken.discard(slot)
 
     def length(self, slot: int) -> int:
         return self.cache.lengths[slot]
@@ -110,6 +114,8 @@ class Runner:
             seen.add(it.slot)
             if it.slot not in self.cache.lengths:
                 raise StepError(f"slot {it.slot} is not open")
+            if it.slot in self._broken:
+                raise StepError(f"slot {it.slot} was left unfinished by a step that failed and can only be closed")
             t = np.asarray(it.tokens, dtype=np.int64).reshape(-1)
             if t.size == 0:
                 raise StepError(f"slot {it.slot} brings no token")
@@ -133,22 +139,33 @@ class Runner:
             out_base.append(acc)
             acc += len(it.want)
         done = [0] * len(items)
-        while True:
-            # one sub-step: up to prefill_chunk tokens of each unfinished sequence, within the budget
-            budget, part = self.max_step_tokens, []
-            for i, t in enumerate(toks):
-                left = t.size - done[i]
-                if left <= 0 or budget <= 0:
-                    continue
-                n = min(left, self.prefill_chunk, budget)
-                part.append((i, done[i], n))
-                budget -= n
-            if not part:
-                break
-            self._run(items, toks, part, out, out_base)
-            for i, _, n in part:
-                done[i] += n
+        before = {it.slot: self.cache.lengths[it.slot] for it in items}
+        try:
+            while True:
+                # one sub-step: up to prefill_chunk tokens of each unfinished sequence, within the budget
+                budget, part = self.max_step_tokens, []
+                for i, t in enumerate(toks):
+                    left = t.size - done[i]
+                    if left <= 0 or budget <= 0:
+                        continue
+                    n = min(left, self.prefill_chunk, budget)
+                    part.append((i, done[i], n))
+                    budget -= n
+                if not part:
+                    break
+                self._run(items, toks, part, out, out_base)
+                for i, _, n in part:
+                    done[i] += n
+        except BaseException:
+            # The step is all or nothing: the lengths go back to what they were, so that they never
+            # name positions no kernel wrote.  What cannot be taken back (a window's ring written
+            # over, a state advanced) leaves the slot fit only for closing.
+            for slot, old in before.items():
+                if slot in self.cache.lengths and not self.cache.rollback(slot, old):
+                    self._broken.add(slot)
+            raise
         self.steps_run += 1
+        self.tokens_run += sum(t.size for t in toks)
         return out
 
     def _run(self, items, toks, part, out, out_base):
@@ -202,7 +219,8 @@ class Runner:
             compute=self.model.compute, act_dtype=self.model.act_dtype, device=self.device, n_tokens=t, n_seqs=b,
             tok_pos=d_pos, tok_seq=d_seq, seq_slot=d_slot, seq_start=d_start, seq_len=d_len, cu_seqlens=d_cu,
             is_decode=bool((lens == 1).all()), max_new=int(lens.max()), max_total=max_total, cache=cache,
-            page_size=cache.page_size)
+            page_size=cache.page_size,
+            host={"seq_slot": slots.tolist(), "seq_start": starts.tolist(), "seq_len": lens.tolist()})
         # the builds whose kernels start under the tail of the kernel before them
         build.set_pdl(True)
         try:
@@ -219,13 +237,16 @@ class Runner:
     # ---- decode steps replayed from CUDA graphs
     def _decode_graph(self, tokens, starts, slots, max_total):
         """One token per sequence through a captured graph.  The batch is padded to a power of
-        two with rows that belong to no sequence: they use the page table's spare row, write into
-        page 0 and read nothing that a real row reads, so they change no result."""
+        two with rows that belong to no sequence: their slot is the spare one (``ctx.pad_slot``:
+        the last row of every page table, all page 0, and of every state tensor), so what they
+        write lands where no sequence reads and they change no result."""
         b = len(tokens)
         bp = 1
         while bp < b:
             bp *= 2
-        len_bucket = 256
+        # one graph per padded batch size; per length bucket as well only when some part's launches
+        # depend on the longest sequence (then ``ctx.max_total`` of the captured step is the bucket)
+        len_bucket = 256 if self._length_matters else self.cache.max_seq_len
         while len_bucket < max_total:
             len_bucket *= 2
         key = (bp, len_bucket)

@@ -24,6 +24,7 @@ import sys
 import torch
 
 from .. import kernels
+from ..cache.pool import PAGE_SIZE
 from .model import build_model
 from .step import Runner, StepItem
 
@@ -38,7 +39,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines=None
     torch.backends.cudnn.allow_tf32 = False
     os.makedirs(out_dir, exist_ok=True)
     model = build_model(model_dir, dtype=dtype, device=device)
-    pages = max(1, (max_tokens + 63) // 64)
+    pages = max(1, -(-max_tokens // PAGE_SIZE))
     runner = Runner(model, max_tokens=max_tokens, max_batch=min(pages, 4096))
     slots = {}
     for line in lines:

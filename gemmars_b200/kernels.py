@@ -56,9 +56,13 @@ def count_launches(n: int) -> None:
     _launches[0] += n
 
 
-# Per-kernel timing for --profile: an event after every launch; the time between two events is
-# put down to the later kernel (kernels of one stream run one after the other).
-_profile = {"on": False, "events": []}
+# Timing for --profile: an event after every launch; the time between two events is put down to
+# the later kernel (kernels of one stream run one after the other).  Every face also says which
+# category its kernel belongs to and how many bytes the launch has to move (weights, inputs,
+# results, cached keys and values where the host knows the lengths), so that the report can give
+# time, calls, bytes and bandwidth per category as the reference's does (src/prof.rs:8-83).
+CATEGORIES = ("matmul", "attention", "norm", "elementwise", "embed", "lm_head", "sampling")
+_profile = {"on": False, "events": [], "category": None}
 
 
 def profile_start() -> None:
@@ -66,40 +70,82 @@ def profile_start() -> None:
     _profile["on"], _profile["events"] = True, []
     ev = torch.cuda.Event(enable_timing=True)
     ev.record()
-    _profile["events"].append(("start", ev))
+    _profile["events"].append(("start", None, 0, ev))
 
 
-def profile_report(steps: int = 1) -> str:
-    """The time per kernel name since profile_start, in the manner of the reference's --profile
-    (src/prof.rs:51-83): ms a step, calls a step, us a call, share."""
+class profile_category:
+    """Within the block, launches are put down to ``name`` whatever their own category (the
+    output head's product is a matmul that the report lists on its own)."""
+
+    def __init__(self, name: str):
+        self.name, self.before = name, None
+
+    def __enter__(self):
+        self.before, _profile["category"] = _profile["category"], self.name
+
+    def __exit__(self, *exc):
+        _profile["category"] = self.before
+
+
+def profile_totals() -> dict:
+    """{"kernels": {name: [calls, ms]}, "categories": {name: [calls, ms, bytes]}} since
+    profile_start; stops collecting.  Synchronizes."""
     _profile["on"] = False
     torch.cuda.synchronize()
     ev = _profile["events"]
-    totals = {}
-    for (_, a), (name, b) in zip(ev, ev[1:]):
-        t = totals.setdefault(name, [0, 0.0])
+    per_kernel, per_cat = {}, {}
+    for (_, _, _, a), (name, cat, nbytes, b) in zip(ev, ev[1:]):
+        ms = a.elapsed_time(b)
+        t = per_kernel.setdefault(name, [0, 0.0])
         t[0] += 1
-        t[1] += a.elapsed_time(b)
-    whole = sum(t[1] for t in totals.values()) or 1.0
-    lines = [f"{'kernel':28s} {'ms/step':>9s} {'calls/step':>11s} {'us/call':>9s} {'share':>7s}"]
-    for name, (calls, ms) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
-        lines.append(f"{name:28s} {ms / steps:9.3f} {calls / steps:11.1f} {ms * 1e3 / calls:9.1f} {100 * ms / whole:6.1f}%")
-    lines.append(f"{'total':28s} {whole / steps:9.3f}")
+        t[1] += ms
+        c = per_cat.setdefault(cat, [0, 0.0, 0])
+        c[0] += 1
+        c[1] += ms
+        c[2] += nbytes
     _profile["events"] = []
+    return {"kernels": per_kernel, "categories": per_cat}
+
+
+def profile_report(tokens: int = 1, totals: Optional[dict] = None) -> str:
+    """The time since profile_start per category and per kernel, in the manner of the
+    reference's --profile (src/prof.rs:51-83): ms a token, calls a token, us a call, and for the
+    categories the bytes a token and the bandwidth they come to.  ``tokens``: the forward tokens
+    that ran meanwhile."""
+    totals = totals or profile_totals()
+    tokens = max(1, tokens)
+    whole = sum(t[1] for t in totals["kernels"].values()) or 1.0
+    lines = [f"[profile over {tokens} forward tokens, {whole / tokens:.3f} ms/token on the device]",
+             f"{'category':14s} {'ms/tok':>9s} {'calls/tok':>10s} {'us/call':>9s} {'MB/tok':>10s} {'GB/s':>8s} {'share':>7s}"]
+    for cat in CATEGORIES + tuple(c for c in totals["categories"] if c not in CATEGORIES):
+        if cat not in totals["categories"]:
+            continue
+        calls, ms, nbytes = totals["categories"][cat]
+        lines.append(f"{str(cat):14s} {ms / tokens:9.4f} {calls / tokens:10.2f} {ms * 1e3 / calls:9.1f} "
+                     f"{nbytes / tokens / 1e6:10.2f} {nbytes / max(ms, 1e-9) / 1e6:8.0f} {100 * ms / whole:6.1f}%")
+    lines.append(f"{'kernel':28s} {'ms/tok':>9s} {'calls/tok':>10s} {'us/call':>9s} {'share':>7s}")
+    for name, (calls, ms) in sorted(totals["kernels"].items(), key=lambda kv: -kv[1][1]):
+        lines.append(f"{name:28s} {ms / tokens:9.4f} {calls / tokens:10.2f} {ms * 1e3 / calls:9.1f} {100 * ms / whole:6.1f}%")
+    lines.append(f"{'total':28s} {whole / tokens:9.4f}")
     return "\n".join(lines)
 
 
-def _check(code: int, what: str):
+def _check(code: int, what: str, category: str = "elementwise", nbytes: int = 0):
     if code == 0:
         _launches[0] += 1
         if _profile["on"]:
             ev = torch.cuda.Event(enable_timing=True)
             ev.record()
-            _profile["events"].append((what, ev))
+            _profile["events"].append((what, _profile["category"] or category, nbytes, ev))
         return
     if code < 0:
         raise KernelError(f"{what}: {_ERRORS.get(code, 'refused')} (code {code})")
     raise KernelError(f"{what}: CUDA launch failed with error {code}")
+
+
+def _nbytes(*tensors) -> int:
+    """Bytes of the given tensors (None counts nothing): what a launch reads and writes."""
+    return sum(t.numel() * t.element_size() for t in tensors if t is not None) if _profile["on"] else 0
 
 
 def _cuda(*tensors):
@@ -135,7 +181,8 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor, s
     f = _fn("elementwise", "gb_embed_gather",
             [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
     _check(f(table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), out.data_ptr(), tokens.numel(),
-             table.shape[1], table.shape[0], scale, _stream()), "embed_gather")
+             table.shape[1], table.shape[0], scale, _stream()), "embed_gather", "embed",
+           _nbytes(out) + tokens.numel() * table.shape[1] * table.element_size())
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
@@ -151,7 +198,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float
     f = _fn("elementwise", "gb_rmsnorm",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p])
     _check(f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype), _ptr(rows_index), rows, n,
-             eps, _stream()), "rmsnorm")
+             eps, _stream()), "rmsnorm", "norm", _nbytes(out, weight) + rows * n * 4)
 
 
 def head_norm_rope_cache(qkv, nh, nkv, hd, rot, q_weight, k_weight, eps, inv_freq, q_scale, tok_pos, tok_seq,
@@ -169,7 +216,9 @@ def head_norm_rope_cache(qkv, nh, nkv, hd, rot, q_weight, k_weight, eps, inv_fre
     _check(f(qkv.data_ptr(), dtype_code(qkv.dtype), qkv.shape[0], nh, nkv, hd, rot, _ptr(q_weight), _ptr(k_weight),
              eps, _ptr(inv_freq), q_scale, tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(),
              _ptr(page_table), page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache),
-             _ptr(vcache), flags, _stream()), "head_norm_rope_cache")
+             _ptr(vcache), flags, _stream()), "head_norm_rope_cache", "elementwise",
+           _nbytes(qkv) * (2 if flags & FLAG_INPLACE else 1)
+           + (qkv.shape[0] * 2 * nkv * hd * qkv.element_size() if flags & FLAG_CACHE else 0))
     if (flags & FLAG_CACHE) and not (flags & FLAG_SINGLE) and nkv > 0 and qkv.shape[0] >= 64:
         count_launches(1)   # prompts: the values go through a second, transposing kernel
 
@@ -180,7 +229,8 @@ def silu_mul(gu: torch.Tensor, out: torch.Tensor):
     inter = out.shape[-1]
     assert gu.shape[-1] == 2 * inter and gu.dtype == out.dtype and gu.is_contiguous() and out.is_contiguous()
     f = _fn("elementwise", "gb_silu_mul", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), out.numel() // inter, inter, _stream()), "silu_mul")
+    _check(f(gu.data_ptr(), out.data_ptr(), dtype_code(out.dtype), out.numel() // inter, inter, _stream()), "silu_mul",
+           "elementwise", _nbytes(gu, out))
 
 
 # --------------------------------------------------------------------------- matrix products
@@ -199,10 +249,26 @@ def gemm_ref(x, w, out, bias=None, accumulate=False):
             [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
              c_longlong, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), dtype_code(x.dtype), _ptr(bias), out.data_ptr(), dtype_code(out.dtype),
-             OUT_ACCUMULATE if accumulate else OUT_STORE, m, n, k, x.stride(0), out.stride(0), _stream()), "gemm_ref")
+             OUT_ACCUMULATE if accumulate else OUT_STORE, m, n, k, x.stride(0), out.stride(0), _stream()), "gemm_ref",
+           "matmul", _nbytes(x, w, bias, out) * 1 + (_nbytes(out) if accumulate else 0))
 
 
-_SM_COUNT = 148
+_sm_counts = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (the current CUDA device when None), read once per
+    device: tile splits, persistent grids and the decode attention's share of the cache are sized
+    by it, so a part with fewer SMs (or a slice of one) is neither oversubscribed nor left idle."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    n = _sm_counts.get(index)
+    if n is None:
+        n = _sm_counts[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return n
+
+
 _TC_MODES = {(torch.bfloat16, False): 0, (torch.float32, False): 1, (torch.float32, True): 2}
 
 
@@ -212,9 +278,11 @@ def gemm_tc_usable(x, w) -> bool:
             and x.stride(0) % 8 == 0 and x.stride(1) == 1 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False):
+def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False, sms: Optional[int] = None):
     """(tokens per tile, K splits) for an [m, k] x [n, k]^T product (``gated``: n features from
-    2n rows, two accumulators per tile)."""
+    2n rows, two accumulators per tile) on a device of ``sms`` multiprocessors (None: the current
+    device's)."""
+    sms = sms or sm_count()
     tiles_n = -(-n // 128)
     if m <= 64:
         bn = 16 if m <= 16 else (32 if m <= 32 else 64)
@@ -225,7 +293,7 @@ def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False):
         # 8 tokens: 6144x4096 22.6/16.1/13.9/12.3, 4096x12288 60/37/24/21; gated 12288x4096 best at 2;
         # 64 tokens: 6144x4096 24.8/21.5/17.0/19.6, 4096x4096 24/22/15/12.6, 4096x12288 63/51/32/25,
         # gated 12288x4096 40/53/53/63.
-        enough = (150 if bn == 16 else 0) if gated else 2 * _SM_COUNT
+        enough = (sms + 2 if bn == 16 else 0) if gated else 2 * sms
         while splits < 8 and tiles * splits < enough and kb // (splits * 2) >= 4:
             splits *= 2
         return bn, splits
@@ -234,9 +302,9 @@ def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False):
     # 384 us with 256-token tiles, 450 us with 128-token tiles
     for bn, tile_eff in ((256, 1.0), (128, 0.85 if gated else 0.92)):
         tiles = tiles_n * -(-m // bn)
-        waves = -(-tiles // _SM_COUNT)
+        waves = -(-tiles // sms)
         fill = m / (-(-m // bn) * bn)
-        score = tile_eff * fill * tiles / (waves * _SM_COUNT)
+        score = tile_eff * fill * tiles / (waves * sms)
         if score > best_score:
             best, best_score = bn, score
     return best, 1
@@ -268,10 +336,11 @@ def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
              c_int, c_int, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
-             bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc")
+             bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc", "matmul",
+           _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
 
 
-def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=_SM_COUNT):
+def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=None):
     """The tensor-core product for prompts (more than 64 rows of x): one CTA per SM walks the output
     tiles, and the epilogue of a tile runs while the next tile's MMAs fill the other accumulator
     buffer.  Operands and modes as gemm_tc."""
@@ -299,7 +368,8 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
              c_int, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0), bn,
-             ctas, _stream()), "gemm_tc_persistent")
+             ctas or sm_count(x.device), _stream()), "gemm_tc_persistent", "matmul",
+           _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
 
 
 # measured on the 8B shape: +1.5 % tokens/s at batch 1 and 8, -1 % at batch 64 (a rank then finishes
@@ -340,7 +410,7 @@ def gemm_qkv(x, w, bias, qkv, nh, nkv, hd, q_weight, k_weight, eps, inv_freq, q_
              bn or auto_bn, splits or auto_splits, _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), eps, q_scale, nh, nkv,
              tok_pos.data_ptr(), _ptr(tok_seq), _ptr(seq_slot), _ptr(page_table),
              page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache), _ptr(vcache), _stream()),
-           "gemm_qkv")
+           "gemm_qkv", "matmul", _nbytes(x, w, bias, qkv))
 
 
 def gemm_swiglu(x, w_gate_up, out):
@@ -393,7 +463,7 @@ def check_status() -> None:
 
 # --------------------------------------------------------------------------- attention
 
-def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None):
+def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None, cache_bytes: int = 0):
     """Causal grouped-query attention of q [T, nh*hd] (row stride free) over the paged cache."""
     _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot)
     nkv, hd = kcache.shape[1], kcache.shape[3]
@@ -403,7 +473,8 @@ def attention_ref(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, to
              c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), dtype_code(q.dtype), kcache.data_ptr(),
              vcache.data_ptr(), page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(),
-             tok_seq.data_ptr(), seq_slot.data_ptr(), q.shape[0], nh, window or 0, _stream()), "attention_ref")
+             tok_seq.data_ptr(), seq_slot.data_ptr(), q.shape[0], nh, window or 0, _stream()), "attention_ref",
+           "attention", _nbytes(q, out) + cache_bytes)
 
 
 def decode_shares(ntok: int, nh: int, nkv: int, longest: int) -> int:
@@ -415,12 +486,12 @@ def decode_shares(ntok: int, nh: int, nkv: int, longest: int) -> int:
     chunks = -(-rep // 16)
     base = max(1, ntok * nkv * chunks)
     blocks = -(-max(longest, 1) // 32)
-    want = (_SM_COUNT + base // 2) // base
+    want = (sm_count() + base // 2) // base
     return max(1, min(want, blocks // 8, 64))
 
 
 def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot, window=None,
-                     shares=1, scratch=None):
+                     shares=1, scratch=None, cache_bytes: int = 0):
     """bfloat16 attention of single positions (one CTA per token, kv head and share of the keys)
     over the paged cache; the unit is compiled for the cache's head size."""
     _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot, scratch)
@@ -439,7 +510,8 @@ def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos,
             defines=(("GB_HEAD_DIM", hd),))
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
              page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(), tok_seq.data_ptr(),
-             seq_slot.data_ptr(), ntok, nh, window or 0, shares, _ptr(scratch), _stream()), "attention_decode")
+             seq_slot.data_ptr(), ntok, nh, window or 0, shares, _ptr(scratch), _stream()), "attention_decode",
+           "attention", _nbytes(q, out) + cache_bytes)
     if shares > 1:
         count_launches(1)   # the merge kernel
 
@@ -456,7 +528,7 @@ def attention_decode_stream_usable(ntok: int, nh: int, nkv: int, hd: int, page_s
 
 
 def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot,
-                            window=None, ctas=None, skip_slot=None):
+                            window=None, ctas=None, skip_slot=None, cache_bytes: int = 0):
     """bfloat16 attention of single positions with the cache streamed through shared memory by
     TMA: the pages that the step reads are dealt evenly to the CTAs as one flat list, whatever the
     lengths of the sequences; parts of a (token, kv head) that fall to different CTAs are added
@@ -477,7 +549,7 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
            c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     f = _fn("attention_decode_stream", "gb_attention_decode_stream", sig, defines=defines)
     if ctas is None:
-        ctas = _SM_COUNT   # measured at 8,192 keys, batch 1 / 8 / 64: 17 / 54 / 323 us; two per SM: 24 / 58 / 329
+        ctas = sm_count(q.device)   # one per SM; measured at 8,192 keys, batch 1 / 8 / 64: 17 / 54 / 323 us; two per SM: 24 / 58 / 329
     need = ctas * 2 * (nh // nkv) * (hd + 2) + ntok + 1
     scratch = _decode_stream_scratch.get(q.device.index)
     if scratch is None or scratch.numel() < need:
@@ -489,7 +561,7 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
              kcache.shape[0], page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(),
              tok_seq.data_ptr(), seq_slot.data_ptr(), ntok, nh, window or 0, -1 if skip_slot is None else skip_slot,
              ctas, scratch.data_ptr(), _stream()),
-           "attention_decode_stream")
+           "attention_decode_stream", "attention", _nbytes(q, out) + cache_bytes)
     count_launches(1)   # the merge kernel
 
 
@@ -497,7 +569,7 @@ def attention_decode_stream_status(reset: bool = True) -> int:
     return _status("gb_attention_decode_stream_status", reset)
 
 
-def attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, cu_seqlens, seq_start, seq_slot, window=None):
+def attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, cu_seqlens, seq_start, seq_slot, window=None, cache_bytes: int = 0):
     """bfloat16 causal attention of packed prompt tokens (sequence b owns tokens cu_seqlens[b] to
     cu_seqlens[b + 1], at positions from seq_start[b]) over the paged cache, which already holds
     the step's own keys and values."""
@@ -512,14 +584,14 @@ def attention_prefill(q, out, nh, kcache, vcache, page_table, page_size, cu_seql
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
              page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, cu_seqlens.data_ptr(),
              seq_start.data_ptr(), seq_slot.data_ptr(), seq_slot.numel(), q.shape[0], nh, window or 0, _stream()),
-           "attention_prefill")
+           "attention_prefill", "attention", _nbytes(q, out) + cache_bytes)
 
 
 TC_PREFILL_HEAD_DIMS = (64, 128)
 
 
 def attention_prefill_tc(q, out, nh, kcache, vcache, page_table, page_size, cu_seqlens, seq_start, seq_slot,
-                         window=None):
+                         window=None, cache_bytes: int = 0):
     """As attention_prefill, on the tcgen05 tensor cores (TMA-fed, S and O in tensor memory); head
     sizes 64 and 128."""
     _cuda(q, out, kcache, vcache, page_table, cu_seqlens, seq_start, seq_slot)
@@ -536,7 +608,7 @@ def attention_prefill_tc(q, out, nh, kcache, vcache, page_table, page_size, cu_s
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
              kcache.shape[0], page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, cu_seqlens.data_ptr(),
              seq_start.data_ptr(), seq_slot.data_ptr(), seq_slot.numel(), q.shape[0], nh, window or 0, _stream()),
-           "attention_prefill_tc")
+           "attention_prefill_tc", "attention", _nbytes(q, out) + cache_bytes)
 
 
 def attention_prefill_tc_status(head_dim: int = 0, reset: bool = True) -> int:
@@ -565,7 +637,8 @@ def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None, 
     f = _fn("sampling", "gb_sample",
             [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
-             _ptr(top_p), _ptr(uniform), out.data_ptr(), _ptr(scratch), _stream()), "sample")
+             _ptr(top_p), _ptr(uniform), out.data_ptr(), _ptr(scratch), _stream()), "sample", "sampling",
+           _nbytes(logits))
     if scratch is not None:
         count_launches(1)
 
@@ -592,11 +665,6 @@ def gemm(x, w, out, bias=None, accumulate=False):
         gemm_ref(x, w, out, bias, accumulate)
 
 
-def extra_units():
-    """Units no model asks for by itself (built with the rest by the build check)."""
-    return []
-
-
 def attention_units(compute: str, head_dim: int):
     if compute == "float32":
         return [("attention_ref", ())]
@@ -612,21 +680,29 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
     """Attention of the step's queries over the cache; picks the kernel for the precision and
     for prompts or single tokens.  float32 always takes the plain kernel, whose arithmetic for a
     position does not depend on the batch."""
+    cached = 0
+    if _profile["on"] and ctx.host is not None:
+        # keys and values the step has to read: each sequence's positions (its window's worth) once
+        per_pos = 2 * kcache.shape[1] * kcache.shape[3] * kcache.element_size()
+        for start, n in zip(ctx.host["seq_start"], ctx.host["seq_len"]):
+            cached += per_pos * (min(start + n, window + n - 1) if window else start + n)
     if q.dtype == torch.bfloat16 and ctx.max_new <= DECODE_KERNEL_MAX_NEW:
         nkv = kcache.shape[1]
         if attention_decode_stream_usable(ctx.n_tokens, nh, nkv, kcache.shape[3], page_size):
             attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq,
-                                    ctx.seq_slot, window, skip_slot=ctx.pad_slot)
+                                    ctx.seq_slot, window, skip_slot=ctx.pad_slot, cache_bytes=cached)
             return
         shares = decode_shares(ctx.n_tokens, nh, nkv, ctx.max_total if window is None else min(ctx.max_total, window))
         attention_decode(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
-                         window, shares)
+                         window, shares, cache_bytes=cached)
         return
     if q.dtype == torch.bfloat16:
         prefill = attention_prefill_tc if kcache.shape[3] in TC_PREFILL_HEAD_DIMS else attention_prefill
-        prefill(q, out, nh, kcache, vcache, page_table, page_size, ctx.cu_seqlens, ctx.seq_start, ctx.seq_slot, window)
+        prefill(q, out, nh, kcache, vcache, page_table, page_size, ctx.cu_seqlens, ctx.seq_start, ctx.seq_slot, window,
+                cache_bytes=cached)
         return
-    attention_ref(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, window)
+    attention_ref(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, window,
+                  cache_bytes=cached)
 
 
 # a step whose sequences bring at most this many tokens each runs the per-position decode kernel

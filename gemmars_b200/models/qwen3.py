@@ -48,6 +48,11 @@ class Qwen3Config(ModelConfig):
     use_sliding_window: bool = key(bool, False)
     sliding_window: Optional[int] = key("opt_int", None)
     layer_types: Optional[List[str]] = key("str_list", None)
+    #: Scaling of the rotation for long contexts (YaRN and the like).  The reference's Qwen path
+    #: does not read it (src/config.rs:490-506 takes rope_theta and partial_rotary_factor only)
+    #: and no part here implements one, so anything but null or the "default" type is refused:
+    #: running such a checkpoint unscaled would give other logits than the model's.
+    rope_scaling: Optional[dict] = key("opt_dict", None)
     model_type: str = key(str, "qwen3")
 
     @classmethod
@@ -60,6 +65,9 @@ class Qwen3Config(ModelConfig):
             for k in ("rope_theta", "partial_rotary_factor"):
                 if rp.get(k) is not None:
                     text[k] = rp[k]
+            kind = rp.get("rope_type", rp.get("type"))
+            if kind not in (None, "default") and text.get("rope_scaling") is None:
+                text["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
             if "text_config" in raw and isinstance(raw["text_config"], dict):
                 raw["text_config"] = text
             else:
@@ -98,6 +106,14 @@ class Qwen3Config(ModelConfig):
                     break
         if self.use_sliding_window and (self.sliding_window is None or self.sliding_window <= 0):
             p.append("use_sliding_window is set but sliding_window is not a positive integer")
+        if self.use_sliding_window and self.layer_types is None:
+            p.append("use_sliding_window is set but layer_types is absent: which layers are windowed is not "
+                     "known (max_window_layers is not read); give layer_types or unset use_sliding_window")
+        if self.rope_scaling is not None:
+            kind = self.rope_scaling.get("rope_type", self.rope_scaling.get("type"))
+            if kind not in (None, "default"):
+                p.append(f"rope_scaling: rotation scaling of type {kind!r} is not implemented "
+                         "(only null or \"default\")")
         return p
 
     @property
@@ -158,8 +174,8 @@ def build_plan(cfg: Qwen3Config, names=None) -> ModelPlan:
                                      "activation": "silu"},
                        {"gate": mp + "gate_proj.weight", "up": mp + "up_proj.weight",
                         "down": mp + "down_proj.weight"})
-        layers.append(LayerSpec(mixer, ffn, norm(lp + "input_layernorm.weight"),
-                                norm(lp + "post_attention_layernorm.weight"), block="prenorm"))
+        layers.append(LayerSpec.prenorm(mixer, ffn, norm(lp + "input_layernorm.weight"),
+                                        norm(lp + "post_attention_layernorm.weight")))
     plan = ModelPlan(
         hidden_size=h, vocab_size=cfg.vocab_size,
         embedding=PartSpec("embedding", {"vocab_size": cfg.vocab_size, "hidden_size": h, "scale": None},

@@ -9,14 +9,15 @@ lo..p of its own sequence (src/model.rs:1187-1226); residual += o Wo^T.
 
 All sizes and constants are parameters: hidden_size, num_heads, num_kv_heads, head_dim,
 qk_norm, qk_norm_eps, bias, window, scale (None: head_dim ** -0.5), position (a PartSpec or
-None), has_kv (False for a layer that only reads another layer's cache).
+None), has_kv (False for a layer that only reads another layer's cache: it has no k and v
+matrices and is given the other layer's keys and values).
 """
 from __future__ import annotations
 
 import torch
 
 from .. import kernels
-from ..cache.pool import KVNeed
+from ..cache.pool import PAGE_SIZE, KVNeed
 from .base import Part, TensorWant, build_part, register_part
 from .linear import Linear
 from .rotary import Rotary
@@ -78,17 +79,25 @@ class Attention(Part):
         return (kernels.gemm_units(self.compute) + [("elementwise", ())]
                 + kernels.attention_units(self.compute, self.head_dim))
 
-    def cache_need(self):
-        return KVNeed(self.num_kv_heads, self.head_dim, self.window) if self.has_kv else None
+    def cache_needs(self):
+        return [KVNeed(self.num_kv_heads, self.head_dim, self.window)] if self.has_kv else []
 
     def weight_bytes(self):
-        return self.qkv.bytes() + self.o.bytes()
+        norms = sum(4 * t.numel() for t in (self.q_norm, self.k_norm if self.has_kv else None) if t is not None)
+        return self.qkv.bytes() + self.o.bytes() + norms
+
+    @property
+    def capture_depends_on_length(self):
+        # the decode kernel that splits the keys over CTAs sizes its split by the longest sequence;
+        # the streaming kernel and the float32 kernel launch the same grid at every length
+        return self.compute == "bfloat16" and not kernels.attention_decode_stream_usable(
+            1, self.num_heads, self.num_kv_heads, self.head_dim, PAGE_SIZE)
 
     # ---- step
-    def forward(self, ctx, h, residual, cache, writes_cache=True):
+    def forward(self, ctx, h, residual, caches, writes_cache=True):
         nh, hd = self.num_heads, self.head_dim
         nkv = self.num_kv_heads if self.has_kv else 0
-        group, kc, vc = cache
+        group, kc, vc = caches[0]
         writes_cache = writes_cache and self.has_kv
         rotary = self.position is None or isinstance(self.position, Rotary)
         rot = self.position.rotary_dim if isinstance(self.position, Rotary) else 0

@@ -55,7 +55,8 @@ class LinearHead(Part):
         return kernels.gemm_units(self.compute)
 
     def forward(self, ctx, h):
-        return self.proj(h, out_dtype=torch.float32)
+        with kernels.profile_category("lm_head"):
+            return self.proj(h, out_dtype=torch.float32)
 
     def weight_bytes(self):
         return self.proj.bytes()

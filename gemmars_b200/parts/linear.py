@@ -31,4 +31,5 @@ class Linear:
         kernels.gemm(x, self.weight, residual, self.bias, accumulate=True)
 
     def bytes(self) -> int:
-        return self.weight.numel() * self.weight.element_size()
+        b = 0 if self.bias is None else self.bias.numel() * self.bias.element_size()
+        return self.weight.numel() * self.weight.element_size() + b

@@ -27,6 +27,9 @@ class RMSNorm(Part):
     def kernel_units(self):
         return [("elementwise", ())]
 
+    def weight_bytes(self):
+        return 0 if self.weight is None else 4 * self.weight.numel()
+
     def forward(self, ctx, x, rows_index=None):
         rows = x.shape[0] if rows_index is None else rows_index.numel()
         out = torch.empty((rows, self.size), dtype=self.act_dtype, device=x.device)

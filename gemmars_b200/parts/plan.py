@@ -26,12 +26,17 @@ class PartSpec:
 
 @dataclasses.dataclass
 class LayerSpec:
-    """A layer: the arrangement (``block`` kind) of a mixer and a feed-forward with their norms."""
-    mixer: PartSpec
-    ffn: PartSpec
-    mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    """A layer: a ``block`` kind and the parts it arranges, by the names that block kind reads.
+    The ``prenorm`` block reads ``mixer_norm, mixer, ffn_norm, ffn``; another arrangement (a third
+    norm, a pair of post-norms, a per-layer input) is another block kind with names of its own,
+    and nothing else has to know them."""
+    parts: Dict[str, PartSpec]
     block: str = "prenorm"
+
+    @classmethod
+    def prenorm(cls, mixer: PartSpec, ffn: PartSpec, mixer_norm: PartSpec, ffn_norm: PartSpec) -> "LayerSpec":
+        """x += mixer(mixer_norm(x)); x += ffn(ffn_norm(x))."""
+        return cls({"mixer_norm": mixer_norm, "mixer": mixer, "ffn_norm": ffn_norm, "ffn": ffn}, "prenorm")
 
 
 @dataclasses.dataclass

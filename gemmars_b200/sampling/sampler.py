@@ -65,6 +65,8 @@ class SamplingParams:
 class BatchSampler:
     """One generator per sequence; ``sample`` draws one token for each given sequence."""
 
+    RING = 4     # pinned host buffers used in turn; one is written again only after its copy is done
+
     def __init__(self, params: Sequence[SamplingParams], device):
         for p in params:
             p.check()
@@ -73,11 +75,38 @@ class BatchSampler:
         self.device = device
         self.all_greedy = all(p.greedy for p in params)
         self.any_wide = any(p.wide for p in params)
+        self._host, self._events, self._turn = None, [None] * self.RING, 0
 
     def sample(self, logits: torch.Tensor, seqs: Sequence[int]) -> List[int]:
         """``logits``: float32 [len(seqs), vocab] on the device; ``seqs``: which sequence each
         row belongs to.  Returns one token id per row."""
         return self.sample_device(logits, seqs).tolist()
+
+    def _stage(self, seqs):
+        """The rows' settings and uniform draws, through pinned host memory that is allocated
+        once for the whole batch (pinning takes about a millisecond, a decode step a few):
+        float32 [3, n] (temperature, top_p, uniform) and int32 [n] (top_k) on the device."""
+        n, cap = len(seqs), len(self.params)
+        if self._host is None:
+            self._host = [(torch.empty(3 * cap, dtype=torch.float32).pin_memory(),
+                           torch.empty(cap, dtype=torch.int32).pin_memory()) for _ in range(self.RING)]
+        i = self._turn
+        self._turn = (i + 1) % self.RING
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        hf, hk = self._host[i]
+        f, k = hf.numpy(), hk.numpy()
+        for j, s in enumerate(seqs):                 # three runs of n values: each copy is one contiguous piece
+            p = self.params[s]
+            f[j], f[n + j] = p.temperature, p.top_p
+            f[2 * n + j] = 0.0 if p.greedy else self.rngs[s].next_f32()
+            k[j] = p.top_k
+        dev_f = hf[:3 * n].to(self.device, non_blocking=True).view(3, n)
+        dev_k = hk[:n].to(self.device, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._events[i] = ev
+        return dev_f, dev_k
 
     def sample_device(self, logits: torch.Tensor, seqs: Sequence[int]) -> torch.Tensor:
         n = len(seqs)
@@ -85,11 +114,6 @@ class BatchSampler:
         if self.all_greedy:
             kernels.sample(logits, out)
             return out
-        temps = [self.params[s].temperature for s in seqs]
-        ks = [self.params[s].top_k for s in seqs]
-        ps = [self.params[s].top_p for s in seqs]
-        us = [0.0 if self.params[s].greedy else self.rngs[s].next_f32() for s in seqs]
-        f = torch.tensor([temps, ps, us], dtype=torch.float32).pin_memory().to(logits.device, non_blocking=True)
-        k = torch.tensor(ks, dtype=torch.int32).pin_memory().to(logits.device, non_blocking=True)
+        f, k = self._stage(seqs)
         kernels.sample(logits, out, f[0], k, f[1], f[2], wide=self.any_wide)
         return out

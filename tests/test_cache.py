@@ -38,14 +38,54 @@ def _cache(needs, max_tokens=64 * 6, slots=4, chunk=64, max_pos=0):
 
 def test_groups_by_need_and_layout():
     full, win = KVNeed(2, 16), KVNeed(2, 16, window=40)
-    c = _cache([(0, win), (1, full), (2, win), (4, StateNeed((3, 5)))])
+    c = _cache([(0, win), (1, [full]), (2, win), (4, StateNeed((3, 5)))])
     assert len(c.kv_groups) == 2 and len(c.state_groups) == 1
-    assert (c.bindings[0].group, c.bindings[0].index) == (0, 0) and (c.bindings[2].group, c.bindings[2].index) == (0, 1)
-    assert c.bindings[1].group == 1 and c.bindings[4].kind == "state"
+    assert (c.bindings[0][0].group, c.bindings[0][0].index) == (0, 0)
+    assert (c.bindings[2][0].group, c.bindings[2][0].index) == (0, 1)
+    assert c.bindings[1][0].group == 1 and c.bindings[4][0].kind == "state"
     g_win, g_full = c.kv_groups
     assert g_full.k.shape == (1, 7, 2, 64, 16) and g_win.k.shape[0] == 2
     assert g_full.table_width == 6 and g_win.table_width == (40 - 1 + 64 + 63) // 64 + 1 == 3
     assert c.state(4).shape == (5, 3, 5)
+
+
+def test_an_entry_may_keep_several_things():
+    """Keys with a state beside them, and two states of different shapes, for one entry; equal
+    needs of different entries share a group."""
+    kv, conv, s = KVNeed(2, 16), StateNeed((3, 8)), StateNeed((4, 4, 2), torch.float32)
+    c = _cache([(0, [kv, conv]), (1, [s, conv]), (2, [kv])])
+    assert len(c.kv_groups) == 1 and c.kv_groups[0].n_layers == 2
+    assert [g.need for g in c.state_groups] == [conv, s]
+    assert [(b.kind, b.group, b.index) for b in c.bindings[0]] == [("kv", 0, 0), ("state", 0, 0)]
+    assert [(b.kind, b.group, b.index) for b in c.bindings[1]] == [("state", 1, 0), ("state", 0, 1)]
+    v0, v1 = c.views(0), c.views(1)
+    assert v0[0][0] is c.kv_groups[0] and v0[0][1].shape == (7, 2, 64, 16) and v0[1].shape == (5, 3, 8)
+    assert v1[0].shape == (5, 4, 4, 2) and v1[1].shape == (5, 3, 8)
+    assert v1[1].data_ptr() != v0[1].data_ptr()                  # same group, a layer of its own
+    assert c.views(7) == []
+    slot = c.open()
+    v1[0][slot] += 1.0
+    c.close(slot)
+    assert c.open() == slot and float(c.views(1)[0][slot].abs().sum()) == 0.0   # cleared when the slot is taken
+
+
+def test_rollback_after_a_failed_step():
+    c = _cache([(0, KVNeed(1, 16))])
+    s = c.open()
+    c.extend(s, 70)
+    held = c.pages_held()
+    c.extend(s, 130)
+    assert c.pages_held() == held + 2
+    assert c.rollback(s, 70) is True and c.lengths[s] == 70 and c.pages_held() == held
+    assert c.extend(s, 1) == 70
+    # a window's ring or a state cannot be put back: the slot's length goes back, its contents may not
+    w = _cache([(0, KVNeed(1, 16, window=40)), (1, StateNeed((2,)))])
+    s = w.open()
+    w.extend(s, 10)
+    w.extend(s, 300)
+    assert w.rollback(s, 10) is False and w.lengths[s] == 10
+    w.close(s)
+    assert w.pages_held() == 0
 
 
 def test_extend_close_accounting_and_ring():

@@ -58,11 +58,24 @@ def test_errors_name_every_key():
     ({"use_sliding_window": True}, "sliding_window"),
     ({"layer_types": ["full_attention"]}, "length mismatch"),
     ({"layer_types": ["full_attention", "linear_attention"]}, "unknown layer type"),
+    # options that change the logits and have no implementation are refused, with the key named
+    ({"use_sliding_window": True, "sliding_window": 8}, "layer_types is absent"),
+    ({"rope_scaling": {"rope_type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"rope_scaling": {"type": "linear", "factor": 2.0}}, "rope_scaling"),
+    ({"rope_parameters": {"rope_theta": 1e6, "rope_type": "yarn", "factor": 4.0}}, "rope_scaling"),
+    ({"rope_scaling": 4}, "rope_scaling"),
 ])
 def test_validation(patch, word):
     with pytest.raises(ConfigError) as e:
         Qwen3Config.from_dict(dict(TINY_A, **patch))
     assert word in str(e.value)
+
+
+def test_null_and_default_rope_scaling_are_accepted():
+    for v in (None, {"rope_type": "default"}, {"type": "default"}):
+        assert Qwen3Config.from_dict(dict(TINY_A, rope_scaling=v)).rope_theta == TINY_A["rope_theta"]
+    ok = Qwen3Config.from_dict(dict(TINY_A, rope_parameters={"rope_theta": 5e5, "rope_type": "default"}))
+    assert ok.rope_theta == 5e5 and ok.rope_scaling is None
 
 
 def test_registry():
@@ -91,8 +104,9 @@ def test_plan_is_data():
     cfg = Qwen3Config.from_dict(TINY_B)
     plan = build_plan(cfg)
     assert len(plan.layers) == 3 and [e.layer for e in plan.schedule] == [0, 1, 2]
-    m = plan.layers[0].mixer
-    assert m.kind == "attention" and m.params["window"] == 40 and plan.layers[1].mixer.params["window"] is None
+    assert plan.layers[0].block == "prenorm" and set(plan.layers[0].parts) == {"mixer_norm", "mixer", "ffn_norm", "ffn"}
+    m = plan.layers[0].parts["mixer"]
+    assert m.kind == "attention" and m.params["window"] == 40 and plan.layers[1].parts["mixer"].params["window"] is None
     assert m.params["num_heads"] == 6 and m.params["num_kv_heads"] == 3 and m.params["head_dim"] == 32
     assert m.params["position"].kind == "rotary" and m.params["position"].params["theta"] == 1e6
     assert m.tensors["q_bias"] == "model.layers.0.self_attn.q_proj.bias"
@@ -103,7 +117,7 @@ def test_plan_is_data():
     names = {"model.language_model.embed_tokens.weight"}
     p2 = build_plan(cfg, names)
     assert p2.head.tensors["weight"] == "model.language_model.embed_tokens.weight"
-    assert p2.layers[2].ffn.tensors["down"] == "model.language_model.layers.2.mlp.down_proj.weight"
+    assert p2.layers[2].parts["ffn"].tensors["down"] == "model.language_model.layers.2.mlp.down_proj.weight"
 
 
 def test_schedule_validation():

@@ -154,7 +154,12 @@ def test_command_line(model_folders, tmp_path):
                        text=True, cwd=ROOT, timeout=300)
     assert p.returncode == 0, p.stderr[-2000:]
     assert [int(x) for x in p.stdout.strip().split(",")] == want
-    assert "ms/step" in p.stderr and "attention_ref" in p.stderr and "gemm_ref" in p.stderr
+    # per category (time, calls, bytes, bandwidth) and per kernel, per forward token
+    assert "ms/tok" in p.stderr and "attention_ref" in p.stderr and "gemm_ref" in p.stderr
+    cats = {l.split()[0]: l.split() for l in p.stderr.splitlines() if l.split() and l.split()[0] in
+            ("matmul", "attention", "norm", "elementwise", "embed", "lm_head", "sampling")}
+    assert set(cats) == {"matmul", "attention", "norm", "elementwise", "embed", "lm_head", "sampling"}
+    assert float(cats["matmul"][4]) > 0 and float(cats["attention"][4]) > 0 and float(cats["lm_head"][5]) > 0
     batch = tmp_path / "batch.txt"
     batch.write_text("1 2 3\n9,8,7,6,5\n")
     p = subprocess.run(base + ["--batch-file", str(batch), "-n", "4"], capture_output=True, text=True, cwd=ROOT,

@@ -122,3 +122,32 @@ def test_slots_are_given_back_when_a_step_fails():
     with pytest.raises(CacheError):
         loop.run([Request([1], 2), Request([2], 2)])
     assert m.slots.free_count == 2
+
+
+def test_a_turn_in_a_kept_slot_uses_the_same_decisions_and_leaves_the_slot_open():
+    """The conversation of ``send``: the loop runs one request in a slot the caller keeps, returns
+    the token that was generated but not run, and the next turn feeds it first."""
+    m = FakeModel(2)
+    slot = m.open()
+    loop = m.loop(max_context=40)
+    first = loop.run_in_slot(slot, 0, Request([3, 4], 3))
+    want, _ = _expected([3, 4], 3)
+    assert first.tokens == want and first.reason == LENGTH and first.unfed == want[-1]
+    assert slot in m.seqs and m.seqs[slot] == [3, 4] + want[:-1]          # the last token was not run
+    # next turn: the unfed token first, then the new ones; a stop token ends it and is not run
+    held = len(m.seqs[slot])
+    feed = [first.unfed, 11]
+    seq = list(m.seqs[slot]) + feed
+    stop_at = sum(seq) % 50
+    second = loop.run_in_slot(slot, held, Request(feed, 5, stop_ids=(stop_at,)))
+    assert second.tokens == [stop_at] and second.reason == STOP and second.unfed is None
+    assert m.seqs[slot] == seq and m.slots.free_count == 1
+    # cancelled: the token the callback saw last is unfed
+    third = loop.run_in_slot(slot, len(seq), Request([1], 9), on_token=lambda i, toks: len(toks) < 2)
+    assert third.reason == CANCELLED and len(third.tokens) == 2 and third.unfed == third.tokens[-1]
+    assert len(m.seqs[slot]) == len(seq) + 1 + 1
+    # the context limit counts what the slot holds already
+    with pytest.raises(ValueError, match="context limit"):
+        loop.run_in_slot(slot, 39, Request([1, 2], 4))
+    m.close(slot)
+    assert m.slots.free_count == 2

@@ -489,3 +489,37 @@ def test_gemm_qkv_against_product_then_head_kernel(k, m, nh, nkv, kk, splits, bi
         assert int((kc.abs().sum(dim=(1, 3)) > 0).sum()) == m    # one row per token and no other
         assert float(kc[0].abs().sum()) == 0.0
     assert k.gemm_tc_status() == 0
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_context_usable(k):
+    """A test build of the product kernel (-DGB_TEST_WITHHOLD_LOAD) never asks for the last block
+    of tokens, so the wait for that block, shortened to 2^14 polls (-DGB_TEST_WAIT_LIMIT), runs
+    out.  The kernel must not hang, trap or fault: it records the wait that gave up in its status
+    word, frees its tensor memory and returns; ``check_status`` then raises, and the next
+    ordinary launch on the same context is right and leaves the word clear."""
+    from ctypes import c_int, c_longlong, c_void_p
+    from gemmars_b200.csrc import build
+    lib = build.load("gemm_tc", (("GB_TEST_WAIT_LIMIT", 1 << 14), ("GB_TEST_WITHHOLD_LOAD", 1)))
+    f = lib.gb_gemm_tc
+    f.restype = c_int
+    f.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+                  c_int, c_int, c_void_p]
+    torch.manual_seed(0)
+    m, n, kk = 8, 256, 512
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
+    out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    assert k.gemm_tc_status() == 0
+    rc = f(x.data_ptr(), w.data_ptr(), None, out.data_ptr(), 0, m, n, kk, x.stride(0), out.stride(0), 16, 1, 4,
+           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0                              # the launch itself is fine
+    torch.cuda.synchronize()                    # and the kernel comes back
+    with pytest.raises(k.KernelError, match="bounded wait ran out.*code 1"):
+        k.check_status()
+    k.check_status()                            # reading the word cleared it
+    good = torch.zeros_like(out)
+    k.gemm_tc(x, w, good)
+    ref = x.float() @ w.float().T
+    assert (good.float() - ref).abs().max().item() <= 2 ** -8 * ref.abs().max().item()
+    assert not torch.equal(good, out)           # the launch that gave up did not finish its product
+    assert k.gemm_tc_status() == 0

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_qwen3 as plain
-from tiny_configs import TINY_B
+from tiny_configs import TINY_B, TOL_BF16
 
 pytestmark = pytest.mark.gpu
 
@@ -50,7 +50,7 @@ def mild_model(tmp_path_factory):
 # bfloat16 rounds q and k to 8 bits, which such scores turn into errors as large as the faults;
 # it runs on the unscaled weights with its usual tolerance, and its attention kernels meet
 # planted far keys in test_kernels_gpu.py, where inputs are the same bfloat16 values on both sides.
-@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", TOL_BF16["B"])])
 def test_long_decoding_and_first_tokens(sharp_model, mild_model, dtype, tol):
     from gemmars_b200.engine import Runner, StepItem, build_model
     folder, toks, ref = sharp_model if dtype == "float32" else mild_model
@@ -89,7 +89,7 @@ def test_sharp_weights_make_faults_visible(sharp_model):
     assert np.abs(changed[-1] - ref[-1]).max() > 1e-3 * np.abs(ref).max()
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", TOL_BF16["B"])])
 def test_prompts_cut_into_chunks_inside_one_step(sharp_model, mild_model, dtype, tol):
     """One step whose prompts are longer than the chunk and than the step's token budget: the
     runner feeds them in sub-steps of its own (some sequences wait for a later sub-step, the window
@@ -123,7 +123,7 @@ def test_prompts_cut_into_chunks_inside_one_step(sharp_model, mild_model, dtype,
         assert np.abs(cut - whole).max() <= tol * scale
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", TOL_BF16["B"])])
 def test_a_batch_of_seventy_sequences(mild_model, dtype, tol):
     """More sequences than the decode kernels' 64-token tiles: the prompts in one step, then single
     tokens for all of them (replayed from a graph padded to 128 rows), then for the half that goes
@@ -164,7 +164,7 @@ def test_a_batch_of_seventy_sequences(mild_model, dtype, tol):
         assert np.abs(new_out[j] - ref[8]).max() <= tol * float(np.abs(ref).max())
 
 
-@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", 2e-2)])
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", TOL_BF16["S128"])])
 def test_heads_of_128_prompt_then_decoding(tmp_path_factory, dtype, tol):
     """A narrow model with heads of 128, so that the engine itself (not only the kernel tests) runs
     the kernels that the released sizes use: a 700-token prompt (tensor-core prompt attention over
@@ -219,5 +219,7 @@ def test_released_width_bfloat16_against_float32():
         res[dtype] = np.concatenate(rows)
         del runner, model
     ref, got = res["float32"], res["bfloat16"]
-    assert np.abs(got - ref).max() <= 2e-2 * np.abs(ref).max()
-    # (with random weights the largest of 151,936 logits leads by less than that: no check of the argmax)
+    assert np.abs(got - ref).max() <= TOL_BF16["S128"] * np.abs(ref).max()
+    # the token either engine would pick is, in the other engine, within that bound of the best
+    for g, r in zip(got, ref):
+        assert r.max() - r[int(g.argmax())] <= TOL_BF16["S128"] * np.abs(ref).max()

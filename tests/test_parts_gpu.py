@@ -26,7 +26,8 @@ def _ctx(runner_or_cache, lengths_before, news, compute="float32", page_size=64)
                        seq_slot=i32(list(range(len(news)))), seq_start=i32(lengths_before), seq_len=i32(news),
                        cu_seqlens=i32(cu), is_decode=all(n == 1 for n in news), max_new=max(news),
                        max_total=max(s + n for s, n in zip(lengths_before, news)), cache=runner_or_cache,
-                       page_size=page_size)
+                       page_size=page_size,
+                       host={"seq_slot": list(range(len(news))), "seq_start": list(lengths_before), "seq_len": list(news)})
 
 
 def test_rmsnorm_part():
@@ -111,7 +112,7 @@ def test_attention_part(window, bias):
                   "v_bias": torch.randn(nkv * hd) * 0.1, "o_bias": torch.randn(h) * 0.1})
     assert set(part.wants()) == set(t)
     part.load({k: v.cuda() for k, v in t.items()})
-    cache = SequenceCache([(0, part.cache_need())], 64 * 4, 2, 0, 64, torch.float32, "cuda")
+    cache = SequenceCache([(0, part.cache_needs())], 64 * 4, 2, 0, 64, torch.float32, "cuda")
     assert cache.kv_groups[0].need.window == window
     slot = cache.open()
     x = torch.randn(45, h, device="cuda")
@@ -126,20 +127,29 @@ def test_attention_part(window, bias):
         cache.extend(slot, n)
         cache.sync()
         ctx = _ctx(cache, [start], [n])
-        part.forward(ctx, x[start:start + n].contiguous(), got[start:start + n], cache.kv(0), True)
+        part.forward(ctx, x[start:start + n].contiguous(), got[start:start + n], cache.views(0), True)
     assert np.abs(got.cpu().numpy() - want).max() < 2e-5
 
 
 # --------------------------------------------------------------------------- parts defined here
 
+FAIL = {"on": False}      # makes the toy mixer raise in the middle of a step
+
+
 def _register_toy_parts():
     from gemmars_b200.cache import StateNeed
     from gemmars_b200.parts import register_part
-    from gemmars_b200.parts.base import Part, TensorWant
+    from gemmars_b200.parts.base import Block, Part, TensorWant
 
     class DecayMixer(Part):
-        """A recurrent toy mixer: s <- s * decay + x W_in per token, in order; out = s W_out.
-        Its state [width] lives in the cache's per-sequence state area."""
+        """A recurrent toy mixer with two states of different shapes per sequence: the last two
+        inputs (a shift register [2, hidden]) and a running sum [width]:
+        u_t = (x_t + x_{t-1} / 2 + x_{t-2} / 4) W_in; s <- s * decay + u_t; out_t = s W_out.
+
+        A step of whole prompts walks each sequence's tokens in order, from the batch's shape on
+        the host (``ctx.host``).  A step of single tokens (which may be a captured one, padded
+        with rows of ``ctx.pad_slot``) is one gather, one update and one scatter by slot, with no
+        question to the host: padding rows read and write the spare row of the states only."""
         category = "mixer"
 
         def __init__(self, spec, compute):
@@ -152,19 +162,35 @@ def _register_toy_parts():
         def load(self, t):
             self.win, self.wout = t["win"].float(), t["wout"].float()
 
-        def cache_need(self):
-            return StateNeed((self.width,))
+        def weight_bytes(self):
+            return 4 * (self.win.numel() + self.wout.numel())
 
-        def forward(self, ctx, h, residual, state, writes_cache=True):
-            u = h.float() @ self.win.T
-            slots, cu = ctx.seq_slot.tolist(), ctx.cu_seqlens.tolist()
-            outs = torch.empty_like(u)
-            for b, slot in enumerate(slots):                 # every sequence's tokens in order, no padding token
-                s = state[slot].clone()
-                for i in range(cu[b], cu[b + 1]):
-                    s = s * self.decay + u[i]
+        def cache_needs(self):
+            return [StateNeed((self.width,)), StateNeed((2, self.h))]
+
+        def forward(self, ctx, h, residual, caches, writes_cache=True):
+            if FAIL["on"]:
+                raise RuntimeError("the toy mixer was told to fail")
+            s_state, shift = caches
+            x = h.float()
+            if ctx.is_decode:
+                slots = ctx.seq_slot.long()
+                reg = shift[slots]
+                s = s_state[slots] * self.decay + (x + 0.5 * reg[:, 0] + 0.25 * reg[:, 1]) @ self.win.T
+                s_state.index_copy_(0, slots, s)
+                shift.index_copy_(0, slots, torch.stack([x, reg[:, 0]], 1))
+                residual += s @ self.wout.T
+                return
+            assert ctx.host is not None and ctx.pad_slot is None       # prompts are never padded
+            outs, at = torch.empty((x.shape[0], self.width), device=x.device), 0
+            for slot, n in zip(ctx.host["seq_slot"], ctx.host["seq_len"]):
+                s, reg = s_state[slot].clone(), shift[slot].clone()
+                for i in range(at, at + n):                 # every sequence's tokens in order
+                    s = s * self.decay + (x[i] + 0.5 * reg[0] + 0.25 * reg[1]) @ self.win.T
+                    reg = torch.stack([x[i], reg[0]])
                     outs[i] = s
-                state[slot] = s
+                s_state[slot], shift[slot] = s, reg
+                at += n
             residual += outs @ self.wout.T
 
     class RoutedFFN(Part):
@@ -181,6 +207,9 @@ def _register_toy_parts():
         def load(self, t):
             self.router, self.experts = t["router"].float(), t["experts"].float()
 
+        def weight_bytes(self):
+            return 4 * (self.router.numel() + self.experts.numel())
+
         def forward(self, ctx, h, residual):
             pick = (h.float() @ self.router.T).argmax(-1)
             residual += torch.einsum("th,tgh->tg", h.float(), self.experts[pick])
@@ -194,22 +223,39 @@ def _register_toy_parts():
             q[:, :, 0] += pos[:, None]
             k[:, :, 0] += pos[:, None]
 
+    class ThreeNormBlock(Block):
+        """Another arrangement: pre-norm as usual, and a third norm on the stream when the layer
+        is done.  It reads a part name (``out_norm``) that the package knows nothing of."""
+
+        def __init__(self, layer_spec, compute):
+            super().__init__(layer_spec, compute)
+            self.built = {"mixer_norm": self.need("mixer_norm", "norm"), "mixer": self.need("mixer", "mixer"),
+                          "ffn_norm": self.need("ffn_norm", "norm"), "ffn": self.need("ffn", "ffn"),
+                          "out_norm": self.need("out_norm", "norm")}
+
+        def parts(self):
+            return self.built
+
+        def forward(self, ctx, x, caches, writes_cache=True):
+            p, mine = self.built, self.split_caches(caches)
+            p["mixer"].forward(ctx, p["mixer_norm"].forward(ctx, x), x, mine["mixer"], writes_cache)
+            p["ffn"].forward(ctx, p["ffn_norm"].forward(ctx, x), x)
+            x.copy_(p["out_norm"].forward(ctx, x))
+
     register_part("mixer", "toy_decay", DecayMixer)
     register_part("ffn", "toy_routed", RoutedFFN)
     register_part("position", "toy_shift", ShiftEncoding)
+    register_part("block", "toy_three_norms", ThreeNormBlock)
 
 
-def test_toy_parts_register_build_and_step():
-    """A model whose layers mix the package's attention (with the toy position encoding) and the toy
-    recurrent mixer, with dense and routed feed-forwards, a layer that runs twice and a layer that
-    reads another's cache: built from a plan, stepped whole, in pieces and batched, with the same
-    result; the recurrent state follows its slot."""
-    from gemmars_b200.engine import Runner, StepItem
+def _toy_model(h=64, vocab=97, width=24):
+    """Layers that mix the package's attention (with the toy position encoding) and the toy
+    recurrent mixer, dense and routed feed-forwards, a block with a third norm, a layer that runs
+    twice and a layer that reads another's cache."""
     from gemmars_b200.engine.model import DecoderModel
     from gemmars_b200.parts import LayerSpec, ModelPlan, PartSpec, ScheduleEntry
     _register_toy_parts()
     torch.manual_seed(4)
-    h, vocab, width = 64, 97, 24
     norm = lambda n: PartSpec("rmsnorm", {"size": h, "eps": 1e-6}, {"weight": n})
     attn = lambda p, pos, kv=True: PartSpec(
         "attention", {"hidden_size": h, "num_heads": 4, "num_kv_heads": 2, "head_dim": 16, "qk_norm": False,
@@ -217,47 +263,132 @@ def test_toy_parts_register_build_and_step():
         {"q": p + "q", "k": p + "k", "v": p + "v", "o": p + "o"} if kv else {"q": p + "q", "o": p + "o"})
     mlp = lambda p: PartSpec("gated_mlp", {"hidden_size": h, "intermediate_size": 96},
                              {"gate": p + "g", "up": p + "u", "down": p + "d"})
+    decay = PartSpec("toy_decay", {"hidden_size": h, "width": width, "decay": 0.9}, {"win": "l1.win", "wout": "l1.wout"})
+    routed = PartSpec("toy_routed", {"hidden_size": h, "experts": 3}, {"router": "l1.r", "experts": "l1.e"})
     layers = [
-        LayerSpec(attn("l0.", PartSpec("toy_shift", {"step": 0.01})), mlp("l0."), norm("l0.n1"), norm("l0.n2")),
-        LayerSpec(PartSpec("toy_decay", {"hidden_size": h, "width": width, "decay": 0.9}, {"win": "l1.win", "wout": "l1.wout"}),
-                  PartSpec("toy_routed", {"hidden_size": h, "experts": 3}, {"router": "l1.r", "experts": "l1.e"}),
-                  norm("l1.n1"), norm("l1.n2")),
-        LayerSpec(attn("l2.", PartSpec("rotary", {"head_dim": 16, "theta": 1e4}), kv=False), mlp("l2."), norm("l2.n1"), norm("l2.n2")),
+        LayerSpec.prenorm(attn("l0.", PartSpec("toy_shift", {"step": 0.01})), mlp("l0."), norm("l0.n1"), norm("l0.n2")),
+        LayerSpec({"mixer": decay, "ffn": routed, "mixer_norm": norm("l1.n1"), "ffn_norm": norm("l1.n2"),
+                   "out_norm": norm("l1.n3")}, block="toy_three_norms"),
+        LayerSpec.prenorm(attn("l2.", PartSpec("rotary", {"head_dim": 16, "theta": 1e4}), kv=False), mlp("l2."),
+                          norm("l2.n1"), norm("l2.n2")),
     ]
-    # layer 1 runs twice (each run with a state of its own); layer 2 reads the cache of entry 0
+    # layer 1 runs twice (each run with states of its own); layer 2 reads the cache of entry 0
     schedule = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2, cache_of=0), ScheduleEntry(1)]
     plan = ModelPlan(h, vocab, PartSpec("embedding", {"vocab_size": vocab, "hidden_size": h}, {"weight": "emb"}),
                      layers, schedule, norm("nf"), PartSpec("linear_head", {"vocab_size": vocab, "hidden_size": h}, {"weight": "emb"}), 0)
     model = DecoderModel(plan, "float32", "cuda:0")
     shapes = model.expected_tensors()
-    assert shapes["l1.e"] == (3, h, h) and "l2.k" not in shapes
+    assert shapes["l1.e"] == (3, h, h) and "l2.k" not in shapes and shapes["l1.n3"] == (h,)
     tensors = {n: (torch.rand(s) + 0.5 if len(s) == 1 else torch.randn(s) * 0.1).cuda() for n, s in shapes.items()}
     model.bind(tensors)
-    needs = model.cache_needs()
-    assert [e for e, _ in needs] == [0, 1, 3]
-    runner = Runner(model, max_tokens=64 * 8, max_batch=4, use_graphs=False)
-    assert len(runner.cache.state_groups) == 1 and runner.cache.state_groups[0].data.shape == (2, 5, width)
-    rng = np.random.default_rng(0)
-    seqs = [rng.integers(0, vocab, n).tolist() for n in (37, 5, 70)]
-    whole = []
+    return model
+
+
+def _whole(runner, seqs):
+    from gemmars_b200.engine import StepItem
+    out = []
     for s in seqs:
         slot = runner.open()
-        whole.append(runner.step([StepItem(slot, s, range(len(s)))]).cpu())
+        out.append(runner.step([StepItem(slot, s, range(len(s)))]).cpu())
         runner.close(slot)
-    # in pieces, batched, unequal; slots reused (their state must start from zero again)
+    return out
+
+
+def _in_pieces(runner, seqs, cut):
+    """The prompts' first ``cut`` tokens in one step, the rest one token a step, as one batch whose
+    shorter sequences end earlier."""
+    from gemmars_b200.engine import StepItem
     slots = [runner.open() for _ in seqs]
-    cut = [30, 1, 64]
     first = runner.step([StepItem(sl, s[:c], range(c)) for sl, s, c in zip(slots, seqs, cut)]).cpu()
-    got = [list(first[sum(cut[:i]):sum(cut[:i + 1])]) for i in range(3)]
+    got = [list(first[sum(cut[:i]):sum(cut[:i + 1])]) for i in range(len(seqs))]
     pos = list(cut)
     while any(p < len(s) for p, s in zip(pos, seqs)):
-        live = [i for i in range(3) if pos[i] < len(seqs[i])]
+        live = [i for i in range(len(seqs)) if pos[i] < len(seqs[i])]
         out = runner.step([StepItem(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu()
         for row, i in zip(out, live):
             got[i].append(row)
             pos[i] += 1
-    for i in range(3):
-        assert (torch.stack(got[i]) - whole[i]).abs().max().item() < 1e-4
     for sl in slots:
         runner.close(sl)
+    return [torch.stack(g) for g in got]
+
+
+@pytest.mark.parametrize("use_graphs", [False, True])
+def test_toy_parts_register_build_and_step(use_graphs):
+    """Built from a plan and stepped whole, in pieces and batched, with the same result; the
+    recurrent states follow their slot and start from zero when a slot is used again.  With
+    captured decode steps the batch of 5, then 4, 3, ... sequences is padded with up to three rows
+    of the spare slot, which must leave every real sequence's state alone."""
+    from gemmars_b200.engine import Runner
+    model = _toy_model()
+    assert [e for e, _ in model.cache_needs()] == [0, 1, 3]
+    assert [len(n) for _, n in model.cache_needs()] == [1, 2, 2]
+    assert model.weight_bytes() > 0 and not model.capture_depends_on_length
+    runner = Runner(model, max_tokens=64 * 12, max_batch=6, use_graphs=use_graphs)
+    shapes = sorted(tuple(g.data.shape) for g in runner.cache.state_groups)
+    assert shapes == [(2, 7, 2, 64), (2, 7, 24)]
+    rng = np.random.default_rng(0)
+    seqs = [rng.integers(0, 97, n).tolist() for n in (37, 5, 70, 12, 9)]
+    whole = _whole(runner, seqs)
+    for round_ in range(2):                      # the second round runs in slots that were used before
+        got = _in_pieces(runner, seqs, [30, 1, 64, 3, 2])
+        for i in range(len(seqs)):
+            assert (got[i] - whole[i]).abs().max().item() < 1e-4, (round_, i)
     assert runner.cache.pages_held() == 0
+    if use_graphs:
+        sizes = sorted(k[0] for k in runner._graphs)                       # one graph per padded batch size,
+        assert 8 in sizes and len(set(sizes)) == len(sizes)                 # whatever the sequences' lengths
+
+
+def test_a_failed_step_takes_nothing_with_it():
+    """A step that raises half way leaves the lengths where they were.  A model that keeps only
+    keys and values goes on as if nothing had happened; one with a state cannot, and its slot
+    refuses further steps until it is closed."""
+    import plain_qwen3 as plain
+    from tiny_configs import TINY_A
+    from gemmars_b200 import kernels
+    from gemmars_b200.engine import Runner, StepItem
+    from gemmars_b200.engine.model import build_model
+    from gemmars_b200.engine.step import StepError
+    from gemmars_b200.weights.random_init import random_weights
+    # keys and values only
+    model = build_model(raw_config=TINY_A, tensors=random_weights(TINY_A, seed=5, device="cuda"), dtype="float32")
+    runner = Runner(model, max_tokens=64 * 8, max_batch=2, use_graphs=False)
+    toks = np.random.default_rng(1).integers(0, TINY_A["vocab_size"], 150).tolist()
+    slot = runner.open()
+    want = _whole(Runner(model, max_tokens=64 * 8, max_batch=2, use_graphs=False), [toks])[0]
+    a = runner.step([StepItem(slot, toks[:70], range(70))]).cpu()
+    held = runner.cache.pages_held()
+    real, calls = kernels.gemm_swiglu, [0]
+
+    def failing(*args, **kw):
+        calls[0] += 1
+        if calls[0] == 2:                       # the second layer's feed-forward: the first layer's keys are written
+            raise kernels.KernelError("made to fail")
+        return real(*args, **kw)
+
+    kernels.gemm_swiglu = failing
+    try:
+        with pytest.raises(kernels.KernelError):
+            runner.step([StepItem(slot, toks[70:], range(80))])
+    finally:
+        kernels.gemm_swiglu = real
+    assert runner.length(slot) == 70 and runner.cache.pages_held() == held
+    b = runner.step([StepItem(slot, toks[70:], range(80))]).cpu()
+    assert torch.equal(torch.cat([a, b]), want)
+    runner.close(slot)
+    # with a state
+    toy = Runner(_toy_model(), max_tokens=64 * 4, max_batch=2, use_graphs=False)
+    slot = toy.open()
+    toy.step([StepItem(slot, [1, 2, 3], [2])])
+    FAIL["on"] = True
+    try:
+        with pytest.raises(RuntimeError, match="told to fail"):
+            toy.step([StepItem(slot, [4], [0])])
+    finally:
+        FAIL["on"] = False
+    assert toy.length(slot) == 3
+    with pytest.raises(StepError, match="can only be closed"):
+        toy.step([StepItem(slot, [4], [0])])
+    toy.close(slot)
+    assert toy.cache.pages_held() == 0 and toy.step([StepItem(toy.open(), [4], [0])]) is not None
