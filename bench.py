@@ -1,16 +1,24 @@
 #!/usr/bin/env python3
-"""Decode and prefill throughput of a Qwen3-8B-shaped model with random weights on one B200.
+"""Decode and prefill throughput of Qwen3-shaped models with random weights on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference] [--config 8b|4b|32b]
 
-A step is one decode step of a batch of 8 sequences at a context of 8,192 tokens.  One JSON
-line is printed: ``value`` = decoded tokens a second measured on the device over exactly K
-steps; ``e2e`` = the same through ``Engine.generate`` (host token ids in, host token ids out,
-every step's host-to-device and device-to-host copies included); ``prefill`` = one prompt of
-2,048 tokens; ``roofline`` = bytes a decode step has to read (every weight once, the cache of
+``--config 8b`` (the default) is the headline benchmark.  A step is one decode step of a batch
+of 8 sequences at a context of 8,192 tokens.  One JSON line is printed: ``value`` = decoded
+tokens a second measured on the device over exactly K steps; ``e2e`` = the same through
+``Engine.generate`` (host token ids in, host token ids out, every step's host-to-device and
+device-to-host copies included) over 256 generated tokens a sequence; ``prefill`` = one prompt
+of 2,048 tokens; ``roofline`` = bytes a decode step has to read (every weight once, the cache of
 the live requests) over its time, against the measured copy bandwidth; ``points`` = decode at
-batch 1 and 64.  Peaks come from MEASURED_PEAKS.json beside this file when it exists, else
-6.65 TB/s and 1.59 PFLOP/s (an earlier measurement on the same pool).
+batch 1 and 64, with the time, bytes, fraction and clocks of each under ``points_detail``.
+
+``--config 4b``: 16 prompts of 128 to 4,096 tokens (uniform, seeded), 256 tokens each at
+temperature 0.7 with a fixed seed, through ``Engine.generate``.  ``--config 32b``: a prompt of
+2,048 tokens, then greedy decoding at batch 1 and 32 up to a context of 4,096.  Each prints one
+line of the same form.
+
+Peaks come from MEASURED_PEAKS.json beside this file when it exists, else 6.65 TB/s and
+1.59 PFLOP/s (an earlier measurement on the same pool).
 """
 from __future__ import annotations
 
@@ -26,17 +34,23 @@ import time
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
-# The layer sizes of the benchmark configuration (Qwen3-8B).
-QWEN3_8B = {
-    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
-    "num_hidden_layers": 36, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8,
-    "head_dim": 128, "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0,
-    "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": False,
-    "max_position_embeddings": 40960,
+
+def _qwen3(layers, hidden, heads, kv_heads, inter, tied):
+    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": layers,
+            "hidden_size": hidden, "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": 128,
+            "intermediate_size": inter, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+            "attention_bias": False, "tie_word_embeddings": tied, "max_position_embeddings": 40960}
+
+
+# The layer sizes of the benchmark configurations (Qwen3-8B is the headline one).
+CONFIGS = {
+    "8b": ("Qwen3-8B shape", _qwen3(36, 4096, 32, 8, 12288, False)),
+    "4b": ("Qwen3-4B shape", _qwen3(36, 2560, 32, 8, 9728, True)),
+    "32b": ("Qwen3-32B shape", _qwen3(64, 5120, 64, 8, 25600, False)),
 }
-FULL_LAYERS = 36
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
+E2E_TOKENS = 256
 
 
 def peaks():
@@ -71,6 +85,7 @@ class ClockSampler:
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
+        return self
 
     def _read(self):
         for line in self.proc.stdout:
@@ -95,9 +110,14 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def kv_bytes_per_token(runner):
+    """Bytes of keys and values one cached position takes over all layers (groups that keep all keys)."""
+    return sum(2 * g.n_layers * g.need.num_kv_heads * g.need.head_dim * g.k.element_size() for g in runner.cache.kv_groups)
+
+
 def decode_bytes(model, runner, lengths):
-    """Bytes one decode step has to read: every weight matrix once and the cached keys and
-    values of the live sequences."""
+    """Bytes one decode step has to read: every weight once and the cached keys and values of
+    the live sequences."""
     kv = 0
     for g in runner.cache.kv_groups:
         per_token = 2 * g.n_layers * g.need.num_kv_heads * g.need.head_dim * g.k.element_size()
@@ -106,12 +126,12 @@ def decode_bytes(model, runner, lengths):
     return model.weight_bytes() + kv
 
 
-def prefill_flops(cfg, layers, t):
+def prefill_flops(cfg, t):
     h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_token = 2 * (h * (nh + 2 * nkv) * hd + nh * hd * h + 3 * h * i)
     attn = 4 * nh * hd * (t * (t + 1) // 2)           # QK^T and PV over the causal half
-    return layers * (per_token * t + attn) + 2 * h * v  # logits of the last row only
+    return cfg["num_hidden_layers"] * (per_token * t + attn) + 2 * h * v  # logits of the last row only
 
 
 def fill_cache(runner, slots, length, real, vocab, gen):
@@ -133,16 +153,20 @@ def fill_cache(runner, slots, length, real, vocab, gen):
                 t[layer].normal_(0.0, 1.0)
 
 
-def time_decode(runner, batch, ctx_end, steps, warmup, real_fill, vocab, sampler_cls, params_cls):
-    """Device time of exactly ``steps`` decode steps of ``batch`` sequences ending at ``ctx_end``."""
+def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs):
+    """Device time of exactly ``steps`` decode steps of ``batch`` sequences ending at ``ctx_end``,
+    with the clocks sampled meanwhile: {"tokens_per_s", "ms_per_step", "steps", "bytes_per_step",
+    "achieved_gbs", "frac", "clocks", "launches"}."""
     import torch
     from gemmars_b200 import kernels
     from gemmars_b200.engine.step import StepItem
+    from gemmars_b200.sampling.sampler import BatchSampler, SamplingParams
+    runner, vocab = eng.runner, eng.model.plan.vocab_size
     gen = torch.Generator().manual_seed(1)
     slots = [runner.open() for _ in range(batch)]
     start_len = ctx_end - steps - warmup
     fill_cache(runner, slots, start_len, real_fill, vocab, gen)
-    sampler = sampler_cls([params_cls()] * batch, runner.device)
+    sampler = BatchSampler([SamplingParams()] * batch, runner.device)
     toks = torch.randint(0, vocab, (batch,), generator=gen).tolist()
 
     def one(toks):
@@ -152,6 +176,7 @@ def time_decode(runner, batch, ctx_end, steps, warmup, real_fill, vocab, sampler
     for _ in range(warmup):
         toks = one(toks).tolist()
     torch.cuda.synchronize()
+    clocks = ClockSampler().start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = kernels.launch_count()
     cur = toks
@@ -160,12 +185,192 @@ def time_decode(runner, batch, ctx_end, steps, warmup, real_fill, vocab, sampler
         cur = one(cur).tolist()          # the next step's tokens come back to the host, as in generation
     e1.record()
     torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    launches = kernels.launch_count() - launches0
+    ms = e0.elapsed_time(e1) / steps
+    clock_rec = clocks.stop()
     lengths = [runner.length(s) for s in slots]
+    nbytes = decode_bytes(eng.model, runner, lengths)
     for s in slots:
         runner.close(s)
-    return ms / steps, launches, lengths
+    kernels.check_status()
+    achieved = nbytes / (ms / 1e3) / 1e9
+    return {"tokens_per_s": round(batch / (ms / 1e3), 1), "ms_per_step": round(ms, 4), "steps": steps,
+            "bytes_per_step": nbytes, "achieved_gbs": round(achieved, 1), "frac": round(achieved / hbm_gbs, 4),
+            "clocks": clock_rec, "launches": kernels.launch_count() - launches0}
+
+
+def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
+    """The median of seven prompts of ``tokens`` tokens after three warm-up prompts."""
+    import torch
+    from gemmars_b200.engine.step import StepItem
+    runner = eng.runner
+    toks = torch.randint(0, cfg["vocab_size"], (tokens,), generator=torch.Generator().manual_seed(3)).tolist()
+    pre_ms = []
+    for it in range(10):
+        s = runner.open()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        runner.step([StepItem(s, toks, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            pre_ms.append(e0.elapsed_time(e1))
+        runner.close(s)
+    pre = statistics.median(pre_ms)
+    frac = prefill_flops(cfg, tokens) / (pre / 1e3) / (tflops * 1e12)
+    return {"value": round(tokens / (pre / 1e3), 1), "tokens": tokens, "ms": round(pre, 3), "frac": round(frac, 4),
+            # a prompt is tens of milliseconds of products under the power cap: also against the sustained rate
+            "frac_sustained": round(frac * tflops / tflops_sustained, 4)}
+
+
+def make_engine(cfg, max_batch, cache_tokens, options=""):
+    import torch
+    from gemmars_b200.engine.engine import Engine, EngineOptions
+    from gemmars_b200.weights.random_init import random_weights
+    torch.cuda.set_device(0)
+    tensors = random_weights(cfg, seed=0, device="cuda:0")
+    opts = EngineOptions.parse({"dtype": "bfloat16", "max_batch": str(max_batch), "max_tokens": str(cache_tokens),
+                                "prefill_chunk": "2048"})
+    for pair in filter(None, (p.strip() for p in options.split(";"))):
+        opts.set(*[x.strip() for x in pair.split("=", 1)])
+    # the engine takes the tensors out of the dict as it binds them, so that a model of 65 GB and
+    # its stacked q/k/v and gate/up copies never sit in memory side by side
+    return Engine.from_config(cfg, tensors, opts, consume=True)
+
+
+def config_record(name, cfg, layers_full, batch, context, fill, peak_line):
+    return {"model": name, "layers": cfg["num_hidden_layers"], "layers_full": layers_full,
+            "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
+            "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "vocab_size": cfg["vocab_size"],
+            "tie_word_embeddings": cfg["tie_word_embeddings"], "global_batch": batch, "seq_len": context,
+            "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU", "cache_fill": fill,
+            "points_cache_fill": "synthetic", "l2": "weights and cache read per step exceed L2 (no flush needed)",
+            "peaks": peak_line}
+
+
+def run_8b(args, name, cfg, layers_full):
+    import torch
+    hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
+    warmup = max(3, args.warmup)
+    points = not args.no_points
+    max_batch = 64 if points else args.batch
+    eng = make_engine(cfg, max_batch, max_batch * (args.context + 64), args.options)
+    vocab = cfg["vocab_size"]
+    # a prompt first: it is a burst of work on a GPU that was waiting
+    prefill = time_prefill(eng, cfg, PREFILL_TOKENS, tflops, tflops_sustained)
+    main = time_decode(eng, args.batch, args.context, args.steps, warmup, args.fill == "real", hbm_gbs)
+
+    # end to end through the entry point: host ids in, host ids out, 256 tokens a sequence
+    gen = torch.Generator().manual_seed(2)
+    e2e_new = max(E2E_TOKENS, args.steps + 1)
+    prompts = [torch.randint(0, vocab, (args.context - e2e_new,), generator=gen).tolist() for _ in range(args.batch)]
+    clocks = ClockSampler().start()
+    res = eng.generate(prompts, max_tokens=e2e_new, stop_ids=[])
+    e2e_clocks = clocks.stop()
+    st = eng.stats
+    assert all(len(r.tokens) == e2e_new for r in res)
+
+    pts, detail = {}, {}
+    if points:
+        for b in (1, 64):
+            d = time_decode(eng, b, args.context, min(args.steps, 16), 3, False, hbm_gbs)
+            pts[f"decode_b{b}"] = d["tokens_per_s"]
+            detail[f"decode_b{b}"] = {k: d[k] for k in ("ms_per_step", "steps", "bytes_per_step", "achieved_gbs", "frac", "clocks")}
+    return {
+        "metric": f"decode tok/s at batch {args.batch}, context {args.context} ({name}, bf16, random weights)",
+        "value": main["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+        "config": config_record(name, cfg, layers_full, args.batch, args.context, args.fill,
+                                f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})"),
+        "clocks": main["clocks"],
+        "e2e": {"value": round(st.generated_tokens / max(st.decode_secs, 1e-9), 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": (8 * args.batch + 1) * 4, "d2h_bytes_per_step": args.batch * 4,
+                "generated": st.generated_tokens, "decode_steps": st.decode_steps,
+                "prefill_secs": round(st.prefill_secs, 3), "sm_mhz": e2e_clocks["sm_mhz"]},
+        "gpu_launches": main["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": main["achieved_gbs"], "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": main["frac"], "bytes_per_step": main["bytes_per_step"]},
+        "points": pts,
+        "points_detail": detail,
+    }
+
+
+def run_4b(args, name, cfg, layers_full):
+    """16 prompts of 128 to 4,096 tokens, 256 tokens each at temperature 0.7, seed fixed, through
+    ``Engine.generate``."""
+    import numpy as np
+    import torch
+    from gemmars_b200.sampling.sampler import SamplingParams
+    hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
+    batch, new = 16, 256
+    rng = np.random.default_rng(4)
+    lengths = [int(x) for x in rng.integers(128, 4097, batch)]
+    eng = make_engine(cfg, batch, batch * (4096 + new + 64), args.options)
+    prompts = [rng.integers(0, cfg["vocab_size"], n).tolist() for n in lengths]
+    sampling = SamplingParams(temperature=0.7, top_k=64, top_p=0.95, seed=42)
+    prefill = time_prefill(eng, cfg, PREFILL_TOKENS, tflops, tflops_sustained)
+    eng.generate([p[:64] for p in prompts], max_tokens=8, sampling=sampling, stop_ids=[])      # warm-up: builds, graphs
+    clocks = ClockSampler().start()
+    res = eng.generate(prompts, max_tokens=new, sampling=sampling, stop_ids=[])
+    clock_rec = clocks.stop()
+    st = eng.stats
+    assert all(len(r.tokens) == new for r in res)
+    # bytes the decode steps had to read: the weights every step, and each sequence's cache as it grows
+    per_tok = kv_bytes_per_token(eng.runner)
+    steps = st.decode_steps
+    kv = sum(per_tok * (n + k) for n in lengths for k in range(1, steps + 1))
+    nbytes = steps * eng.model.weight_bytes() + kv
+    achieved = nbytes / max(st.decode_secs, 1e-9) / 1e9
+    ms = st.decode_secs * 1e3 / max(steps, 1)
+    value = st.generated_tokens / max(st.decode_secs, 1e-9)
+    return {
+        "metric": f"decode tok/s, 16 prompts of 128-4096 tokens, 256 tokens each at temperature 0.7 ({name}, bf16, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": 8,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+        "config": dict({k: v for k, v in config_record(name, cfg, layers_full, batch, max(lengths) + new, "real",
+                                                       f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})").items()
+                        if k not in ("cache_fill", "points_cache_fill")},
+                       prompt_tokens=sum(lengths), mean_prompt=round(sum(lengths) / batch, 1),
+                       sampling="temperature 0.7, top_k 64, top_p 0.95, seed 42", timing="wall clock through Engine.generate"),
+        "clocks": clock_rec,
+        "e2e": {"value": round(value, 1), "unit": "tokens/s", "h2d_bytes_per_step": (8 * batch + 1) * 4 + 16 * batch,
+                "d2h_bytes_per_step": batch * 4, "generated": st.generated_tokens, "decode_steps": steps,
+                "prefill_secs": round(st.prefill_secs, 3),
+                "prefill_tokens_per_s": round(sum(lengths) / max(st.prefill_secs, 1e-9), 1)},
+        "gpu_launches": None,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": round(achieved / hbm_gbs, 4), "bytes_per_step": nbytes // max(steps, 1)},
+        "points": {},
+    }
+
+
+def run_32b(args, name, cfg, layers_full):
+    """A prompt of 2,048 tokens, then greedy decoding at batch 1 and 32 up to a context of 4,096."""
+    hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
+    context, steps, warmup = 4096, args.steps, max(3, args.warmup)
+    eng = make_engine(cfg, 32, 32 * (context + 64), args.options)
+    prefill = time_prefill(eng, cfg, PREFILL_TOKENS, tflops, tflops_sustained)
+    main = time_decode(eng, 32, context, steps, warmup, args.fill == "real", hbm_gbs)
+    one = time_decode(eng, 1, context, steps, warmup, args.fill == "real", hbm_gbs)
+    keep = ("ms_per_step", "steps", "bytes_per_step", "achieved_gbs", "frac", "clocks")
+    return {
+        "metric": f"decode tok/s at batch 32, context {context} ({name}, bf16, random weights)",
+        "value": main["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random weights, random token ids",
+        "config": config_record(name, cfg, layers_full, 32, context, args.fill,
+                                f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})"),
+        "clocks": main["clocks"], "gpu_launches": main["launches"], "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": main["achieved_gbs"], "peak": hbm_gbs, "unit": "GB/s",
+                     "frac": main["frac"], "bytes_per_step": main["bytes_per_step"]},
+        "points": {"decode_b1": one["tokens_per_s"], "decode_b32": main["tokens_per_s"]},
+        "points_detail": {"decode_b1": {k: one[k] for k in keep}, "decode_b32": {k: main[k] for k in keep}},
+    }
 
 
 def main():
@@ -174,9 +379,10 @@ def main():
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--config", choices=sorted(CONFIGS), default="8b", help="which model shape and workload")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (named in config)")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--fill", choices=["real", "synthetic"], default="real",
                     help="how the cache is brought to the context length before decoding is timed")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
@@ -190,104 +396,10 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported", flush=True)
         return 2
-    warmup = max(3, args.warmup)
-
-    import torch
-    from gemmars_b200 import kernels
-    from gemmars_b200.engine.engine import Engine, EngineOptions
-    from gemmars_b200.engine.step import StepItem
-    from gemmars_b200.sampling.sampler import BatchSampler, SamplingParams
-    from gemmars_b200.weights.random_init import random_weights
-
-    hbm_gbs, tflops, tflops_sustained, peak_src = peaks()
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
-    vocab = cfg["vocab_size"]
-    torch.cuda.set_device(0)
-    tensors = random_weights(cfg, seed=0, device="cuda:0")
-    points = not args.no_points
-    max_batch = 64 if points else args.batch
-    cache_tokens = max_batch * (args.context + 64)
-    opts = EngineOptions.parse({"dtype": "bfloat16", "max_batch": str(max_batch), "max_tokens": str(cache_tokens),
-                                "prefill_chunk": "2048"})
-    for pair in filter(None, (p.strip() for p in args.options.split(";"))):
-        opts.set(*[x.strip() for x in pair.split("=", 1)])
-    eng = Engine.from_config(cfg, tensors, opts)
-    del tensors
-    runner, model = eng.runner, eng.model
-
-    # ---- prefill of 2,048 tokens (first: a prompt is a burst of work on a GPU that was waiting)
-    toks = torch.randint(0, vocab, (PREFILL_TOKENS,), generator=torch.Generator().manual_seed(3)).tolist()
-    pre_ms = []
-    for it in range(10):
-        s = runner.open()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        runner.step([StepItem(s, toks, [PREFILL_TOKENS - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        if it >= 3:                        # three warm-up prompts
-            pre_ms.append(e0.elapsed_time(e1))
-        runner.close(s)
-    pre = statistics.median(pre_ms)
-    pre_frac = prefill_flops(cfg, args.layers, PREFILL_TOKENS) / (pre / 1e3) / (tflops * 1e12)
-
-    # ---- the timed decode steps (device time, CUDA events)
-    clocks = ClockSampler()
-    clocks.start()
-    ms_step, launches, lengths = time_decode(runner, args.batch, args.context, args.steps, warmup,
-                                             args.fill == "real", vocab, BatchSampler, SamplingParams)
-    clock_rec = clocks.stop()
-    value = args.batch / (ms_step / 1e3)
-    step_bytes = decode_bytes(model, runner, lengths)
-    achieved = step_bytes / (ms_step / 1e3) / 1e9
-
-    # ---- end to end through the entry point: host ids in, host ids out
-    gen = torch.Generator().manual_seed(2)
-    e2e_new = args.steps + 1
-    prompt_len = args.context - e2e_new
-    prompts = [torch.randint(0, vocab, (prompt_len,), generator=gen).tolist() for _ in range(args.batch)]
-    res = eng.generate(prompts, max_tokens=e2e_new, stop_ids=[])
-    st = eng.stats
-    e2e_value = st.generated_tokens / max(st.decode_secs, 1e-9)
-    h2d = (8 * args.batch + 1) * 4
-    d2h = args.batch * 4
-
-    pts = {}
-    if points:
-        for b in (1, 64):
-            ms_b, _, _ = time_decode(runner, b, args.context, min(args.steps, 16), 3, False, vocab, BatchSampler,
-                                     SamplingParams)
-            pts[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
-
-    line = {
-        "metric": "decode tok/s at batch 8, context 8192 (Qwen3-8B shape, bf16, random weights)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
-        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: random weights, random token ids",
-        "config": {
-            "model": "Qwen3-8B shape", "layers": args.layers, "layers_full": FULL_LAYERS,
-            "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
-            "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
-            "head_dim": cfg["head_dim"], "vocab_size": vocab, "global_batch": args.batch, "seq_len": args.context,
-            "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU", "cache_fill": args.fill,
-            "points_cache_fill": "synthetic", "l2": "weights and cache read per step exceed L2 (no flush needed)",
-            "peaks": f"{hbm_gbs:.0f} GB/s, {tflops:.0f} TFLOP/s ({peak_src})",
-        },
-        "clocks": clock_rec,
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "generated": st.generated_tokens,
-                "prefill_secs": round(st.prefill_secs, 3)},
-        "gpu_launches": launches,
-        "prefill": {"value": round(PREFILL_TOKENS / (pre / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre, 3),
-                    "frac": round(pre_frac, 4),
-                    # the prompt is a 30 ms run of products under the power cap: also against the sustained rate
-                    "frac_sustained": round(pre_frac * tflops / tflops_sustained, 4)},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_gbs, "unit": "GB/s",
-                     "frac": round(achieved / hbm_gbs, 4), "bytes_per_step": step_bytes},
-        "points": pts,
-    }
-    assert all(len(r.tokens) == e2e_new for r in res)
+    name, cfg = CONFIGS[args.config]
+    layers_full = cfg["num_hidden_layers"]
+    cfg = dict(cfg, num_hidden_layers=args.layers or layers_full)
+    line = {"8b": run_8b, "4b": run_4b, "32b": run_32b}[args.config](args, name, cfg, layers_full)
     print(json.dumps(line), flush=True)
     return 0
 

@@ -138,10 +138,13 @@ class Engine:
         return cls(build_model(model, dtype=opts.dtype, device=opts.device), opts, folder=model)
 
     @classmethod
-    def from_config(cls, raw_config: dict, tensors: dict, options=None) -> "Engine":
-        """An engine over tensors given directly ({checkpoint name: tensor}), e.g. random weights."""
+    def from_config(cls, raw_config: dict, tensors: dict, options=None, consume: bool = False) -> "Engine":
+        """An engine over tensors given directly ({checkpoint name: tensor}), e.g. random weights.
+        With ``consume`` the tensors are taken out of the dict as they are bound, so that a large
+        model and the stacked copies made of it never lie in memory side by side."""
         opts = EngineOptions.parse(options)
-        return cls(build_model(raw_config=raw_config, tensors=tensors, dtype=opts.dtype, device=opts.device), opts)
+        return cls(build_model(raw_config=raw_config, tensors=tensors, dtype=opts.dtype, device=opts.device,
+                               consume=consume), opts)
 
     # ---- settings
     def set(self, key: str, value) -> None:

@@ -68,21 +68,40 @@ class DecoderModel:
                     units.append(u)
         return units
 
-    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+    def bind(self, tensors: Dict[str, torch.Tensor], consume: bool = False) -> None:
         """Gives every part its tensors: matrices in the compute precision, vectors in float32.
         A matrix stored in 32-bit is rounded to bfloat16 for the bfloat16 engine, as the
-        reference does for its bf16 matmuls (src/safetensors.rs:707-733)."""
+        reference does for its bf16 matmuls (src/safetensors.rs:707-733).  With ``consume`` a
+        tensor leaves ``tensors`` when the last part that wants it has been given it: parts that
+        stack matrices (q/k/v, gate/up) make copies, and the originals are then freed part by
+        part instead of all at the end."""
+        uses = {}
+        for part, spec in self.named_parts():
+            for short in part.wants():
+                name = spec.tensors.get(short)
+                if name is not None:
+                    uses[name] = uses.get(name, 0) + 1
         converted = {}
 
         def get(name, role):
             want = torch.float32 if role == "vector" else self.act_dtype
             key = (name, want)
-            if key not in converted:
+            t = converted.get(key)
+            if t is None:
                 t = tensors[name]
                 if t.device != self.device:
                     t = t.to(self.device)
-                converted[key] = t if t.dtype == want else t.to(want)
-            return converted[key]
+                if t.dtype != want:
+                    t = t.to(want)
+                if uses[name] > 1:
+                    converted[key] = t          # tied tensors: the same device tensor for every user
+            uses[name] -= 1
+            if uses[name] == 0:
+                for k in [k for k in converted if k[0] == name]:
+                    del converted[k]
+                if consume:
+                    del tensors[name]
+            return t
 
         for part, spec in self.named_parts():
             mine = {}
@@ -91,7 +110,7 @@ class DecoderModel:
                 if name is not None and name in tensors:
                     mine[short] = get(name, want.role)
             part.load(mine)
-        converted.clear()
+            del mine
 
     # ---- cache needs of the schedule
     def cache_needs(self):
@@ -141,7 +160,7 @@ class DecoderModel:
 
 def build_model(folder: Optional[str] = None, *, raw_config: Optional[dict] = None,
                 tensors: Optional[Dict[str, torch.Tensor]] = None, dtype: str = "bfloat16",
-                device="cuda:0", compile_kernels: bool = True) -> DecoderModel:
+                device="cuda:0", compile_kernels: bool = True, consume: bool = False) -> DecoderModel:
     """The model of a folder (config.json + safetensors), or of ``raw_config`` with ``tensors``
     given directly ({checkpoint name: tensor}, e.g. random weights made on the device)."""
     from .. import models  # noqa: F401  (registers the architectures)
@@ -167,5 +186,5 @@ def build_model(folder: Optional[str] = None, *, raw_config: Optional[dict] = No
     else:
         check_checkpoint({n: tuple(t.shape) for n, t in tensors.items()}, expected, ignored, where="(given tensors)")
         loaded = tensors
-    model.bind(loaded)
+    model.bind(loaded, consume=consume or files is not None)
     return model

@@ -122,7 +122,7 @@ def profile_report(tokens: int = 1, totals: Optional[dict] = None) -> str:
             continue
         calls, ms, nbytes = totals["categories"][cat]
         lines.append(f"{str(cat):14s} {ms / tokens:9.4f} {calls / tokens:10.2f} {ms * 1e3 / calls:9.1f} "
-                     f"{nbytes / tokens / 1e6:10.2f} {nbytes / max(ms, 1e-9) / 1e6:8.0f} {100 * ms / whole:6.1f}%")
+                     f"{nbytes / tokens / 1e6:10.4f} {nbytes / max(ms, 1e-9) / 1e6:8.1f} {100 * ms / whole:6.1f}%")
     lines.append(f"{'kernel':28s} {'ms/tok':>9s} {'calls/tok':>10s} {'us/call':>9s} {'share':>7s}")
     for name, (calls, ms) in sorted(totals["kernels"].items(), key=lambda kv: -kv[1][1]):
         lines.append(f"{name:28s} {ms / tokens:9.4f} {calls / tokens:10.2f} {ms * 1e3 / calls:9.1f} {100 * ms / whole:6.1f}%")
