@@ -619,28 +619,48 @@ def attention_prefill_tc_status(head_dim: int = 0, reset: bool = True) -> int:
 # --------------------------------------------------------------------------- sampling
 
 _sample_scratch = {}
+_sample_cut_scratch = {}
 
 
-def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None, wide=False):
+def sample(logits, out, temperature=None, top_k=None, top_p=None, uniform=None, wide=False, cap: Optional[int] = None):
     """out[r] = token drawn from logits[r] (float32 [rows, vocab]).  Rows whose temperature is
-    <= 0 (or all rows when ``temperature`` is None) take the first maximum.  Rows with top_k = 0
-    (all tokens) or more than MAX_TOP_K candidates need ``wide``: they are sorted in scratch memory
-    of 20 bytes per logit."""
+    <= 0 (or all rows when ``temperature`` is None) take the first maximum.  ``cap``: the largest
+    top_k among the rows that have one from 1 to MAX_TOP_K (None: MAX_TOP_K when any row is
+    sampled, 1 when all are greedy); a smaller cap is less work.  Rows with top_k = 0 (all tokens)
+    or more than MAX_TOP_K candidates need ``wide``: they are sorted in scratch memory of 20 bytes
+    per logit."""
     _cuda(logits, out, temperature, top_k, top_p, uniform)
     assert logits.dtype == torch.float32 and logits.stride(-1) == 1 and out.dtype == torch.int32
+    rows, vocab = logits.shape
+    if cap is None:
+        cap = 1 if temperature is None else MAX_TOP_K
+    cap = max(1, min(int(cap), MAX_TOP_K))
+    sms = sm_count(logits.device)
+    size = _fn("sampling", "gb_sample_scratch_bytes", [c_int, c_int, c_int, c_int])
+    size.restype = c_longlong
+    need = size(rows, vocab, cap, sms)
+    if need < 0:
+        raise KernelError(f"sample: a vocabulary of {vocab} with up to {cap} candidates a row is not supported "
+                          "(at most 64 slices of 16,384 tokens, whose candidates together number at most 16,384)")
+    cut = _sample_cut_scratch.get(logits.device.index)
+    if cut is None or cut.numel() < need:
+        if cut is not None:
+            _outgrown.append(cut)         # a captured step may still point at it: never freed
+        cut = _sample_cut_scratch[logits.device.index] = torch.empty(max(need, 1 << 20), dtype=torch.uint8,
+                                                                     device=logits.device)
     scratch = None
     if wide and temperature is not None:
-        need = 5 * logits.shape[0] * logits.shape[1]
+        need = 5 * rows * vocab
         scratch = _sample_scratch.get(logits.device.index)
         if scratch is None or scratch.numel() < need:
             scratch = _sample_scratch[logits.device.index] = torch.empty(need, dtype=torch.float32, device=logits.device)
     f = _fn("sampling", "gb_sample",
-            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(logits.data_ptr(), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
-             _ptr(top_p), _ptr(uniform), out.data_ptr(), _ptr(scratch), _stream()), "sample", "sampling",
-           _nbytes(logits))
-    if scratch is not None:
-        count_launches(1)
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_void_p])
+    _check(f(logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(top_k),
+             _ptr(top_p), _ptr(uniform), out.data_ptr(), _ptr(scratch), cut.data_ptr(), cap, sms, _stream()),
+           "sample", "sampling", _nbytes(logits))
+    count_launches(1 if scratch is None else 2)
 
 
 # --------------------------------------------------------------------------- choices by precision and shape

@@ -75,6 +75,9 @@ class BatchSampler:
         self.device = device
         self.all_greedy = all(p.greedy for p in params)
         self.any_wide = any(p.wide for p in params)
+        # the most candidates a row served from shared memory can have: the device kernels do less
+        # work for a smaller bound
+        self.cap = max([p.top_k for p in params if not p.greedy and not p.wide] + [1])
         self._host, self._events, self._turn = None, [None] * self.RING, 0
 
     def sample(self, logits: torch.Tensor, seqs: Sequence[int]) -> List[int]:
@@ -115,5 +118,5 @@ class BatchSampler:
             kernels.sample(logits, out)
             return out
         f, k = self._stage(seqs)
-        kernels.sample(logits, out, f[0], k, f[1], f[2], wide=self.any_wide)
+        kernels.sample(logits, out, f[0], k, f[1], f[2], wide=self.any_wide, cap=self.cap)
         return out

@@ -109,6 +109,44 @@ def test_device_sampler_matches_the_plain_sampler():
     assert out.tolist() == [plain.argmax(r) for r in logits]
 
 
+def test_device_sampler_at_a_released_vocabulary():
+    """Sixteen rows of 151,936 logits: every row is cut into slices that different CTAs select
+    from, so the candidates of a row come from several CTAs; ties are planted across the slices'
+    borders and at the k-th place.  Token for token against the plain sampler."""
+    from gemmars_b200 import kernels
+    rng = np.random.default_rng(6)
+    rows, vocab = 16, 151936
+    logits = (rng.standard_normal((rows, vocab)) * 2.5).astype(np.float32)
+    top = float(logits.max()) + 1.0
+    logits[0, [5, 40000, 151935]] = top                              # equal maxima far apart: the lowest id first
+    logits[1, 9000:9100] = logits[1, 120000:120050] = 4.0            # 150 equal values around the 64-th place
+    logits[2, ::1000] = top                                          # 152 equal maxima, k = 100
+    logits[3, 151935] = top                                          # the last token of the last slice
+    params = [(0.0, 64, 0.95), (0.8, 64, 0.95), (1.0, 100, 1.0), (0.0, 1, 1.0)] + [
+        (0.6 + 0.1 * i, [1, 7, 64, 333, 1024][i % 5], [0.5, 0.9, 0.95, 1.0][i % 4]) for i in range(12)]
+    dev = torch.from_numpy(logits).cuda()
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    for trial in range(6):
+        samplers = [plain.Sampler(t, k, p, seed=trial * 31 + i + 1) for i, (t, k, p) in enumerate(params)]
+        us = []
+        for s in samplers:
+            state = s.rng
+            us.append(float(s.next_f32()) if s.temperature > 0 else 0.0)
+            s.rng = state
+        args = (torch.tensor([p[0] for p in params], dtype=torch.float32, device="cuda"),
+                torch.tensor([p[1] for p in params], dtype=torch.int32, device="cuda"),
+                torch.tensor([p[2] for p in params], dtype=torch.float32, device="cuda"),
+                torch.tensor(us, dtype=torch.float32, device="cuda"))
+        kernels.sample(dev, out, *args, cap=1024)
+        want = [s.sample(logits[i]) for i, s in enumerate(samplers)]
+        assert out.tolist() == want, f"trial {trial}"
+    kernels.sample(dev, out)                                           # all greedy
+    assert out.tolist() == [int(np.argmax(r)) for r in logits]
+    # a cap below a row's top_k would drop candidates: the sampler object computes it from its rows
+    from gemmars_b200.sampling.sampler import BatchSampler, SamplingParams
+    assert BatchSampler([SamplingParams(0.7, 64), SamplingParams(0.0, 900), SamplingParams(1.0, 0)], "cuda").cap == 64
+
+
 def test_temperature_sampling_is_seeded(model_folders):
     from gemmars_b200 import Engine, SamplingParams
     folder = model_folders(TINY_A)
