@@ -289,11 +289,21 @@ def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False, sms: Optional[in
         tiles, kb = tiles_n, -(-k // 64)
         splits = 1
         # too few tiles to keep every SM streaming: split the inner dimension over a cluster, whose
-        # ranks each add a share of the tile's tokens.  Measured with cold weights (us, 1/2/4/8 splits):
-        # 8 tokens: 6144x4096 22.6/16.1/13.9/12.3, 4096x12288 60/37/24/21; gated 12288x4096 best at 2;
-        # 64 tokens: 6144x4096 24.8/21.5/17.0/19.6, 4096x4096 24/22/15/12.6, 4096x12288 63/51/32/25,
-        # gated 12288x4096 40/53/53/63.
-        enough = (sms + 2 if bn == 16 else 0) if gated else 2 * sms
+        # ranks each add a share of the tile's tokens.  The CTAs wanted in all: two per SM for tiles of
+        # 16 tokens, one per SM for wider tiles (every split sends all the tile's tokens' partial sums
+        # once more through the cluster, which costs more the more tokens there are), about one per
+        # SM for the gated product with 16 tokens and no split above that.  Measured with cold
+        # weights at the layer sizes of 4B / 8B / 32B models (us, 1/2/4/8 splits):
+        #  8 tokens: 6144x4096 22.6/15.4/13.6/12.8, 4096x12288 59/33/23/21, 10240x5120 28/23/21/24,
+        #            gated 12288x4096 40/36/40/40, gated 25600x5120 82/86/86/95;
+        # 32 tokens: 6144x2560 16/14/12/16, 6144x4096 23/17/16/18, 10240x5120 29/25/30/32,
+        #            5120x8192 42/30/21/25, 5120x25600 121/72/51/58, 2560x4096 23/18/12/11;
+        # 64 tokens: 6144x4096 23/20/18/23, 4096x4096 23/23/16/15, 10240x5120 30/29/34/39,
+        #            5120x25600 122/83/58/63, gated 12288x4096 42/60/61/88.
+        if gated:
+            enough = sms + 2 if bn == 16 else 0
+        else:
+            enough = 2 * sms if bn == 16 else sms
         while splits < 8 and tiles * splits < enough and kb // (splits * 2) >= 4:
             splits *= 2
         return bn, splits
@@ -372,16 +382,21 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
            _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
 
 
-# measured on the 8B shape: +1.5 % tokens/s at batch 1 and 8, -1 % at batch 64 (a rank then finishes
-# eight tokens one after the other, three barriers each)
-QKV_FUSED_MAX_TOKENS = 32
+# measured inside replayed steps: +1.5 % tokens/s at batch 1 and 8 (8B layer sizes), even at batch 16
+# (4B), -1.5 % at batch 24 (8B), -2.5 % at batch 32 (32B), -1 % at batch 64 (8B): a rank finishes
+# its share of the tokens one after the other, three barriers each
+QKV_FUSED_MAX_TOKENS = 16
 
 
-def gemm_qkv_usable(x, w, nh: int, nkv: int, hd: int, rot: int) -> bool:
+QKV_KERNEL_MAX_TOKENS = 64     # what the kernel takes; the dispatch stops earlier, where it stops paying
+
+
+def gemm_qkv_usable(x, w, nh: int, nkv: int, hd: int, rot: int, limit: Optional[int] = None) -> bool:
     """Whether the q/k/v product of a step can do the per-head work in its epilogue: a decode step
-    in bfloat16 with heads of 128 (a head is a tile of the product), rotated over all dims or not
-    at all."""
-    return (x.dtype == torch.bfloat16 and x.shape[0] <= QKV_FUSED_MAX_TOKENS and hd == 128 and rot in (0, hd)
+    in bfloat16 of at most ``limit`` tokens (None: as many as it pays for) with heads of 128 (a
+    head is a tile of the product), rotated over all dims or not at all."""
+    limit = QKV_FUSED_MAX_TOKENS if limit is None else limit
+    return (x.dtype == torch.bfloat16 and x.shape[0] <= limit and hd == 128 and rot in (0, hd)
             and w.shape[0] == (nh + 2 * nkv) * hd and gemm_tc_usable(x, w))
 
 
@@ -394,8 +409,8 @@ def gemm_qkv(x, w, bias, qkv, nh, nkv, hd, q_weight, k_weight, eps, inv_freq, q_
     m, k = x.shape
     n = w.shape[0]
     assert qkv.dtype == torch.bfloat16 and qkv.shape == (m, n) and qkv.stride(1) == 1 and w.is_contiguous()
-    if not gemm_qkv_usable(x, w, nh, nkv, hd, hd if inv_freq is not None else 0):
-        raise KernelError(f"gemm_qkv: needs bfloat16, at most {QKV_FUSED_MAX_TOKENS} tokens and heads of 128")
+    if not gemm_qkv_usable(x, w, nh, nkv, hd, hd if inv_freq is not None else 0, limit=QKV_KERNEL_MAX_TOKENS):
+        raise KernelError(f"gemm_qkv: needs bfloat16, at most {QKV_KERNEL_MAX_TOKENS} tokens and heads of 128")
     if page_table is not None:
         assert kcache.dtype == torch.bfloat16 and kcache.is_contiguous() and kcache.shape[1:] == (nkv, page_size, hd)
         assert vcache.is_contiguous() and vcache.shape[1:] == (nkv, hd, page_size)
