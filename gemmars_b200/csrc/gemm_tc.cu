@@ -58,6 +58,7 @@ struct QkvTail {
   bf16* vcache;
   float eps, q_scale;
   int nh, nkv, table_width, page_size;
+  const float2* rope_table; // prompts: [tokens][64] (cos, sin) of each packed token's angles, or null
 };
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
 
@@ -101,8 +102,10 @@ struct TileOut {
   __device__ __forceinline__ TileOut(const CUtensorMap* m, uint8_t* staging, int warp)
       : map(m), pieces(staging + warp * PIECES * SLOT_BYTES), sent(0) {}
   __device__ __forceinline__ static void put(uint8_t* p, int token, int lane, float r) {
-    if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16) ((bf16*)p)[token * FEATURES + lane] = __float2bfloat16_rn(r);
-    else ((float*)p)[token * FEATURES + lane] = r;
+    if (MODE == EPI_STORE_BF16 || MODE == EPI_SWIGLU_BF16 || MODE == EPI_QKV_BF16)
+      ((bf16*)p)[token * FEATURES + lane] = __float2bfloat16_rn(r);
+    else
+      ((float*)p)[token * FEATURES + lane] = r;
   }
   // the piece to fill next; waits until the request that last used its memory has read it
   __device__ __forceinline__ uint8_t* next(int lane) {
@@ -244,6 +247,124 @@ __device__ __forceinline__ void qkv_finish(const QkvTail& tl, void* y, long long
   const bf16 o = __float2bfloat16_rn(r);
   if (is_q || !tl.page_table) ((bf16*)y)[(size_t)m * ldy + n0 + f] = o;
   else tl.kcache[(cache_row * tl.page_size + pos % tl.page_size) * BM + f] = o;
+}
+
+// ---- the same per-head work for prompts, in the persistent kernel's epilogue -------------------
+// There a warp holds, for its lane's feature, 32 tokens of the tile at a time (x[0..31]), and the
+// four epilogue warps together hold the head's 128 features of those tokens.
+//
+// Sum over the warp's 32 lanes of each of 32 values, lane l ending up with the sum of value l:
+// at every step a lane keeps one half of its values and gives the other half to its partner,
+// 31 shuffles in all instead of five per value.
+__device__ __forceinline__ float lanes_sum_32(float (&v)[32], int lane) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < off; ++i) {
+      const float give = upper ? v[i] : v[i + off];
+      const float keep = upper ? v[i + off] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, give, off);
+    }
+  }
+  return v[0];
+}
+
+// Shared memory of the prompt tail: the epilogue warps' exchange (the other half of a rotation
+// pair lives 64 features away, in warp w ^ 2; value tiles are transposed through the same memory)
+// and the warps' partial sums of squares.
+struct PromptTailShared {
+  float* exchange;   // [4 warps][32 tokens][32 lanes]
+  float* partial;    // [4 warps][32 tokens]
+};
+
+// One round: tokens m_first .. m_first + 31 of head `head` (features 32 * warp + lane), the raw
+// products in x.  Queries leave through `tile_out`; keys and values go to the cache.
+template <int MODE, int SLOT>
+__device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[32], int head, int warp, int lane, int m_first,
+                                                 int M, int Nq, const PromptTailShared& sh, TileOut<MODE, SLOT>& tile_out) {
+  const int f = warp * 32 + lane;
+  const bool is_q = head < tl.nh, is_k = !is_q && head < tl.nh + tl.nkv;
+  // where this lane's token (m_first + lane) lives in the cache: its row of positions
+  int cache_row = 0, pos_in_page = 0;
+  if (!is_q) {
+    const int m = min(m_first + lane, M - 1);
+    const int pos = tl.tok_pos[m], slot = tl.seq_slot[tl.tok_seq[m]];
+    const int page = tl.page_table[(size_t)slot * tl.table_width + (pos / tl.page_size) % tl.table_width];
+    pos_in_page = pos % tl.page_size;
+    cache_row = page * tl.nkv + (head - tl.nh - (is_k ? 0 : tl.nkv));
+  }
+  if (!is_q && !is_k) {
+    // ---- a value head: as it is, transposed into the page ([dim][position]).  Through shared
+    // memory, so that a store covers 8 positions of one dim (16 bytes) where the 32 tokens are
+    // consecutive positions of one page that start on a multiple of 8.
+    bf16* mine = (bf16*)(sh.exchange + warp * 32 * 32);      // [32 features][32 tokens]
+#pragma unroll
+    for (int j = 0; j < 32; ++j) mine[lane * 32 + j] = __float2bfloat16_rn(x[j]);
+    __syncwarp();
+    const int row0 = __shfl_sync(0xffffffffu, cache_row, 0), p0 = __shfl_sync(0xffffffffu, pos_in_page, 0);
+    const bool run = __all_sync(0xffffffffu, cache_row == row0 && pos_in_page == p0 + lane) && (p0 & 7) == 0 &&
+                     m_first + 31 < M;
+    if (run) {
+      const int fl = lane >> 2, ch = lane & 3;              // 8 features an instruction, 4 chunks of 8 tokens
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int ff = 8 * i + fl;
+        const uint4 v = *(const uint4*)(mine + ff * 32 + 8 * ch);
+        *(uint4*)(tl.vcache + ((size_t)row0 * BM + warp * 32 + ff) * tl.page_size + p0 + 8 * ch) = v;
+      }
+    } else {
+      for (int j = 0; j < 32; ++j) {
+        const int row = __shfl_sync(0xffffffffu, cache_row, j), pp = __shfl_sync(0xffffffffu, pos_in_page, j);
+        if (m_first + j < M) tl.vcache[((size_t)row * BM + f) * tl.page_size + pp] = mine[lane * 32 + j];
+      }
+    }
+    __syncwarp();
+    return;
+  }
+  // ---- a query or key head: RMSNorm over the head's 128 features, per token
+  const float* w = is_q ? tl.q_weight : tl.k_weight;
+  if (w) {
+    float sq[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) sq[j] = x[j] * x[j];
+    sh.partial[warp * 32 + lane] = lanes_sum_32(sq, lane);     // token `lane`, this warp's 32 features
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const float total = sh.partial[lane] + sh.partial[32 + lane] + sh.partial[64 + lane] + sh.partial[96 + lane];
+    const float inv = 1.0f / sqrtf(total / (float)BM + tl.eps), wf = w[f];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) x[j] = x[j] * __shfl_sync(0xffffffffu, inv, j) * wf;
+  }
+  // ---- rotation: dims i and i + 64 are a pair (a, b): a' = a cos - b sin, b' = b cos + a sin
+  if (tl.rope_table) {
+    float* mine = sh.exchange + warp * 32 * 32;
+    const float* theirs = sh.exchange + (warp ^ 2) * 32 * 32;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) mine[j * 32 + lane] = x[j];
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const float2* tab = tl.rope_table + (f & 63);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float2 cs = tab[(size_t)min(m_first + j, M - 1) * 64];
+      const float other = theirs[j * 32 + lane];
+      x[j] = f < 64 ? x[j] * cs.x - other * cs.y : x[j] * cs.x + other * cs.y;
+    }
+  }
+  if (is_q) {
+    uint8_t* p = tile_out.next(lane);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) tile_out.put(p, j, lane, x[j] * tl.q_scale);
+    tile_out.post(p, lane, head * BM + warp * 32, m_first, Nq);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int row = __shfl_sync(0xffffffffu, cache_row, j), pp = __shfl_sync(0xffffffffu, pos_in_page, j);
+      if (m_first + j < M) tl.kcache[((size_t)row * tl.page_size + pp) * BM + f] = __float2bfloat16_rn(x[j]);
+    }
+  }
+  // With both steps on, the barrier of each keeps the other's memory safe for the next round;
+  // with one alone, a warp could write the next round's values while another still reads these.
+  if ((w != nullptr) != (tl.rope_table != nullptr)) asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -531,8 +652,10 @@ template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
-                          void* __restrict__ y, int M, int N, int K, long long ldy, int bn) {
+                          void* __restrict__ y, int M, int N, int K, long long ldy, int bn,
+                          const __grid_constant__ QkvTail tail) {
   constexpr bool GATED = MODE == EPI_SWIGLU_BF16;   // rows of a tile: 16 gate, 16 up, ... (see gate_rows)
+  constexpr bool QKV = MODE == EPI_QKV_BF16;        // a tile is one head: norm, rotation, cache write (qkv_prompt_round)
   constexpr int TILE_F = GATED ? BM / 2 : BM;       // features of the result per tile
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
@@ -550,8 +673,12 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   uint8_t* out_staging = smem + STAGES * STAGE_BYTES + 1024;   // past the barriers; OUT_STAGING_BYTES
   // gated: the pieces are 16 tokens of bfloat16 (1 KB), and the pairs' exchange has the upper half
-  constexpr int SLOT = GATED ? OUT_STAGING_BYTES / 2 / (4 * PIECES) : PIECE_BYTES;
+  constexpr int SLOT = (GATED || QKV) ? OUT_STAGING_BYTES / 2 / (4 * PIECES) : PIECE_BYTES;
   static_assert(!GATED || (SLOT >= 16 * PIECE_FEATURES * 2 && OUT_STAGING_BYTES / 2 >= EXCHANGE_BYTES), "gated staging");
+  // q/k/v: bfloat16 pieces of 32 tokens in the lower half, the warps' exchange in the upper half,
+  // their partial sums behind the barriers
+  static_assert(!QKV || (SLOT >= PIECE_TOKENS * PIECE_FEATURES * 2 && OUT_STAGING_BYTES / 2 >= 4 * 32 * 32 * 4), "q/k/v staging");
+  static_assert((2 * STAGES + 4) * 8 + 16 + 4 * 32 * 4 <= 1024, "the barriers and the partial sums have 1 KB");
   __shared__ int epilogue_gave_up;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -652,6 +779,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     const bool is_up = GATED && warp >= 2;
     TileOut<MODE, SLOT> tile_out(&map_y, out_staging, warp);
     GateExchange exchange(out_staging + OUT_STAGING_BYTES / 2, warp);
+    const PromptTailShared tail_shared{(float*)(out_staging + OUT_STAGING_BYTES / 2),
+                                       (float*)((uint8_t*)tmem_slot + 16)};
     const bool both = bn % 32 == 0;   // 32 tokens per round; the result's map is cut to match
     uint32_t i = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
@@ -661,7 +790,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       const int n = n0 + f;
       bool have = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1));
       if (!have && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
-      if (GATED) {   // the warps of a pair meet at barriers below: they leave together or not at all
+      if (GATED || QKV) {   // the warps meet at barriers below: they leave together or not at all
         if (!have && lane == 0) epilogue_gave_up = 1;
         asm volatile("bar.sync 3, 128;" ::: "memory");
         have = epilogue_gave_up == 0;
@@ -700,6 +829,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                 if (row + j < M) emit<MODE>(y, (size_t)(row + j) * ldy + n, r[j]);
             }
           }
+        } else if (QKV) {
+          float x[32];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            x[j] = __uint_as_float(v[j]) + bv;
+            x[16 + j] = __uint_as_float(v2[j]) + bv;
+          }
+          qkv_prompt_round<MODE, SLOT>(tail, x, n0 / BM, warp, lane, m0 + c, M, tail.nh * BM, tail_shared, tile_out);
         } else if (y_tma) {
           tile_out.send(v, v2, both, bv, lane, n0 + warp * 32, m0 + c, N);
         } else {
@@ -711,12 +848,25 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
     }
-    if (y_tma) tile_out.finish(lane);
+    if (y_tma || QKV) tile_out.finish(lane);
   }
   tc_fence_before();
   __syncthreads();
   __syncwarp();
   if (warp == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+}
+
+// cos and sin of every packed token's angles, once per step for all layers: table[t][i] =
+// (cos, sin)(float32(position of t) * inv_freq[i]) (src/kernels.rs:1525-1531).
+__global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ table, int ntok, int half) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= ntok * half) return;
+  float s, c;
+  sincosf((float)tok_pos[i / half] * inv_freq[i % half], &s, &c);
+  table[i] = make_float2(c, s);
 }
 
 // ------------------------------------------------------------------ host side
@@ -781,7 +931,7 @@ int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const Ou
 
 template <int BN, int STAGES, int MODE>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
-                      int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream) {
+                      int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
   // stages, 1 KB of barriers, the pieces on their way out, 1 KB to align the base
   constexpr size_t SMEM = (size_t)STAGES * ((size_t)BM * BK * 2 + BN * BK * 2) + 1024 + OUT_STAGING_BYTES + 1024;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
@@ -796,7 +946,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
   }
   const int tiles = ((M + bn - 1) / bn) * ((N + TILE_F - 1) / TILE_F);
   gb_launch(kernel, dim3(tiles < ctas ? tiles : ctas), dim3(THREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N,
-            K, ldy, bn);
+            K, ldy, bn, tail);
   return gb_launch_status();
 }
 
@@ -914,6 +1064,45 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
   return GB_ERR_ARG;
 }
 
+// (cos, sin) of every packed token's angles: table [ntok][half] float2, for gb_gemm_tc_qkv_prompt.
+GB_EXPORT int gb_rope_table(const int* tok_pos, const float* inv_freq, void* table, int ntok, int half,
+                            cudaStream_t stream) {
+  if (ntok <= 0 || half <= 0) return 0;
+  if (!tok_pos || !inv_freq || !table) return GB_ERR_ARG;
+  const long long total = (long long)ntok * half;
+  gb_launch(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, tok_pos, inv_freq,
+            (float2*)table, ntok, half);
+  return gb_launch_status();
+}
+
+// The q/k/v product of a prompt step (more than 64 tokens) with the per-head work in its epilogue
+// (head size 128): y [M, nh * 128] (rows ldy apart) gets the queries, normed, rotated and scaled;
+// the keys (normed, rotated) and the values go straight into the paged cache, which must be
+// given.  q_weight / k_weight null: no norm; rope_table ([M][64] (cos, sin), see gb_rope_table)
+// null: no rotation.  ctas: CTAs to launch.
+GB_EXPORT int gb_gemm_tc_qkv_prompt(const void* x, const void* w, const float* bias, void* y, int M, int N, int K,
+                                    long long ldx, long long ldy, int ctas, const float* q_weight, const float* k_weight,
+                                    const void* rope_table, float eps, float q_scale, int nh, int nkv, const int* tok_pos,
+                                    const int* tok_seq, const int* seq_slot, const int* page_table, int table_width,
+                                    int page_size, void* kcache, void* vcache, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return GB_ERR_SIZE;
+  if (nh <= 0 || nkv < 0 || N != (nh + 2 * nkv) * BM || !tok_pos) return GB_ERR_SIZE;
+  if (nkv > 0 && (!tok_seq || !seq_slot || !page_table || !kcache || !vcache || page_size <= 0 || (page_size % 8)))
+    return GB_ERR_ARG;
+  if ((q_weight == nullptr) != (k_weight == nullptr)) return GB_ERR_ARG;
+  if ((ldy % 8) || ((uintptr_t)y & 15)) return GB_ERR_SIZE;    // the queries leave by TMA
+  const int bn = M <= 128 ? 128 : 256;
+  CUtensorMap mw, mx;
+  if (!tensor_map(&mw, w, (uint64_t)N, (uint64_t)K, (uint64_t)K * 2, BM)) return GB_ERR_ARG;
+  if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
+  const OutMap my = out_map(y, EPI_STORE_BF16, M, nh * BM, ldy, 32);
+  if (!my.usable) return GB_ERR_ARG;
+  QkvTail tail{q_weight, k_weight, nullptr, tok_pos, tok_seq, seq_slot, page_table, (bf16*)kcache, (bf16*)vcache,
+               eps, q_scale, nh, nkv, table_width, page_size, (const float2*)rope_table};
+  if (bn > 128) return launch_persistent<256, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
+  return launch_persistent<128, 6, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
+}
 
 // The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator).
 // Synchronizes the device; for tests and health checks, not for the step.

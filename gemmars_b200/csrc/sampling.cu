@@ -36,7 +36,7 @@ __device__ __forceinline__ int candidate_token(unsigned long long c) { return (i
 struct SelectShared {
   int hist[256];
   unsigned long long prefix;
-  int remaining, count;
+  int remaining, count, done;
 };
 
 // The k largest of the block's values (v[e] of every thread; 0 = no value; all others differ),
@@ -44,7 +44,7 @@ struct SelectShared {
 // Radix selection of the k-th largest from the top byte down, then one pass that collects.
 __device__ void select_largest(const unsigned long long (&v)[PER_THREAD], int k, unsigned long long* out, SelectShared& s) {
   const int tid = threadIdx.x, lane = tid & 31;
-  if (tid == 0) { s.prefix = 0ull; s.remaining = k; s.count = 0; }
+  if (tid == 0) { s.prefix = 0ull; s.remaining = k; s.count = 0; s.done = 0; }
   for (int pass = 0; pass < 8; ++pass) {
     const int shift = 56 - 8 * pass;
     if (tid < 256) s.hist[tid] = 0;
@@ -55,12 +55,16 @@ __device__ void select_largest(const unsigned long long (&v)[PER_THREAD], int k,
     for (int e = 0; e < PER_THREAD; ++e) {
       const bool in = v[e] != 0ull && (v[e] & mask) == prefix;
       const int bin = (int)((v[e] >> shift) & 255);
-      // lanes that count into the same bin send one addition: the logits of a row share their top
-      // bytes, and thirty-two additions to one address would run one after the other
-      const unsigned active = __ballot_sync(0xffffffffu, in);
-      if (in) {
-        const unsigned same = __match_any_sync(active, bin);
-        if (lane == __ffs(same) - 1) atomicAdd(&s.hist[bin], __popc(same));
+      if (pass == 0) {
+        // the logits of a row share their top byte: lanes that count into the same bin send one
+        // addition, where thirty-two additions to one address would run one after the other
+        const unsigned active = __ballot_sync(0xffffffffu, in);
+        if (in) {
+          const unsigned same = __match_any_sync(active, bin);
+          if (lane == __ffs(same) - 1) atomicAdd(&s.hist[bin], __popc(same));
+        }
+      } else if (in) {
+        atomicAdd(&s.hist[bin], 1);     // further down the values spread over the bins
       }
     }
     __syncthreads();
@@ -79,18 +83,30 @@ __device__ void select_largest(const unsigned long long (&v)[PER_THREAD], int k,
       const unsigned reached = __ballot_sync(0xffffffffu, incl >= remaining);
       const int owner = reached ? __ffs(reached) - 1 : 31;
       if (lane == owner) {
-        int left = remaining - (incl - sum), j = 0;
-        for (; j < 7; ++j) {
-          if (mine[j] >= left) break;
-          left -= mine[j];
+        int left = remaining - (incl - sum), j = 7, in_bin = mine[7];
+        bool found = false;
+#pragma unroll
+        for (int q = 0; q < 7; ++q) {
+          if (!found) {
+            if (mine[q] >= left) {
+              found = true;
+              j = q;
+              in_bin = mine[q];
+            } else {
+              left -= mine[q];
+            }
+          }
         }
         s.prefix = prefix | ((unsigned long long)(255 - 8 * lane - j) << shift);
         s.remaining = left;
+        // every value of the chosen bin is wanted: the bytes below cannot change the answer
+        s.done = in_bin == left;
       }
     }
     __syncthreads();
+    if (s.done) break;
   }
-  const unsigned long long kth = s.prefix;
+  const unsigned long long kth = s.prefix;      // the k-th largest, or (stopped early) its leading bytes
 #pragma unroll
   for (int e = 0; e < PER_THREAD; ++e)
     if (v[e] != 0ull && v[e] >= kth) {

@@ -128,6 +128,10 @@ class DecoderModel:
     def forward(self, ctx: StepContext, tokens: torch.Tensor) -> torch.Tensor:
         """Runs the step's packed tokens through the schedule; returns the float32 residual
         stream [T, H] before the final norm."""
+        # what the parts keep for the length of a step (a table of angles shared by the layers) is
+        # made anew by every run: a context that is run again, eagerly and then under capture,
+        # must launch the kernels that fill it again
+        ctx.extras.clear()
         x = torch.empty((tokens.numel(), self.plan.hidden_size), dtype=torch.float32, device=self.device)
         self.embedding.forward(ctx, tokens, x)
         for i, e in enumerate(self.plan.schedule):

@@ -428,6 +428,56 @@ def gemm_qkv(x, w, bias, qkv, nh, nkv, hd, q_weight, k_weight, eps, inv_freq, q_
            "gemm_qkv", "matmul", _nbytes(x, w, bias, qkv))
 
 
+def rope_table(tok_pos, inv_freq):
+    """[tokens, half] pairs (cos, sin) of float32(position) * inv_freq, float32 [tokens, half, 2]:
+    the angles of a step's packed tokens, computed once for all layers."""
+    _cuda(tok_pos, inv_freq)
+    assert tok_pos.dtype == torch.int32 and inv_freq.dtype == torch.float32
+    ntok, half = tok_pos.numel(), inv_freq.numel()
+    table = torch.empty((ntok, half, 2), dtype=torch.float32, device=tok_pos.device)
+    f = _fn("gemm_tc", "gb_rope_table", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(tok_pos.data_ptr(), inv_freq.data_ptr(), table.data_ptr(), ntok, half, _stream()), "rope_table",
+           "elementwise", _nbytes(table))
+    return table
+
+
+def gemm_qkv_prompt_usable(x, w, nh: int, nkv: int, hd: int, rot: int, page_size: int) -> bool:
+    """Whether the q/k/v product of a prompt step can do the per-head work in its epilogue:
+    bfloat16, more than 64 tokens, heads of 128 rotated over all dims or not at all."""
+    return (x.dtype == torch.bfloat16 and x.shape[0] > 64 and hd == 128 and rot in (0, hd) and page_size % 8 == 0
+            and w.shape[0] == (nh + 2 * nkv) * hd and gemm_tc_usable(x, w))
+
+
+def gemm_qkv_prompt(x, w, bias, q_out, nh, nkv, hd, q_weight, k_weight, eps, table, q_scale, tok_pos, tok_seq, seq_slot,
+                    page_table, page_size, kcache, vcache, ctas=None):
+    """q_out[:, :nh*hd] = a prompt step's queries, normed per head, rotated and scaled; the keys
+    (normed, rotated) and the values go into the paged cache: the q/k/v product of more than 64
+    tokens and head_norm_rope_cache in one kernel.  ``table``: rope_table of the step's tokens
+    (None: no rotation).  See gemm_qkv_prompt_usable."""
+    _cuda(x, w, bias, q_out, q_weight, k_weight, table, tok_pos, tok_seq, seq_slot, page_table, kcache, vcache)
+    m, k = x.shape
+    n = w.shape[0]
+    assert q_out.dtype == torch.bfloat16 and q_out.shape == (m, nh * hd) and q_out.stride(1) == 1 and w.is_contiguous()
+    if not gemm_qkv_prompt_usable(x, w, nh, nkv, hd, hd if table is not None else 0, page_size):
+        raise KernelError("gemm_qkv_prompt: needs bfloat16, more than 64 tokens and heads of 128")
+    if nkv:
+        assert kcache.dtype == torch.bfloat16 and kcache.is_contiguous() and kcache.shape[1:] == (nkv, page_size, hd)
+        assert vcache.is_contiguous() and vcache.shape[1:] == (nkv, hd, page_size)
+    if table is not None:
+        assert table.dtype == torch.float32 and table.shape == (m, hd // 2, 2) and table.is_contiguous()
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == n
+    f = _fn("gemm_tc", "gb_gemm_tc_qkv_prompt",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
+             c_void_p, c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+             c_void_p, c_void_p])
+    _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), q_out.data_ptr(), m, n, k, x.stride(0), q_out.stride(0),
+             ctas or sm_count(x.device), _ptr(q_weight), _ptr(k_weight), _ptr(table), eps, q_scale, nh, nkv,
+             tok_pos.data_ptr(), _ptr(tok_seq), _ptr(seq_slot), _ptr(page_table),
+             page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache), _ptr(vcache), _stream()),
+           "gemm_qkv_prompt", "matmul", _nbytes(x, w, bias, q_out) + m * 2 * nkv * hd * 2)
+
+
 def gemm_swiglu(x, w_gate_up, out):
     """out[M, N] = silu(x @ gate.T) * (x @ up.T) for w_gate_up = [gate; up] of 2N rows: one
     tensor-core kernel in bfloat16; two kernels (product, then activation) otherwise."""

@@ -114,6 +114,20 @@ class Attention(Part):
             kernels.attention(ctx, qkv[:, :nh * hd], att, nh, kc, vc, group.page_table, group.page_size, self.window)
             self.o.add_into(att, residual)
             return
+        if (rotary and writes_cache == self.has_kv
+                and kernels.gemm_qkv_prompt_usable(h, self.qkv.weight, nh, nkv, hd, rot, group.page_size)):
+            # a prompt step with heads of 128: the same on the prompt product's epilogue; the queries
+            # are all that is written out, keys and values go straight into the cache
+            q = torch.empty((h.shape[0], nh * hd), dtype=h.dtype, device=h.device)
+            kernels.gemm_qkv_prompt(h, self.qkv.weight, self.qkv.bias, q, nh, nkv, hd,
+                                    self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None,
+                                    self.eps, self.position.table(ctx) if rot else None, self.scale, ctx.tok_pos,
+                                    ctx.tok_seq, ctx.seq_slot, group.page_table if nkv else None, group.page_size,
+                                    kc if nkv else None, vc if nkv else None)
+            att = torch.empty_like(q)
+            kernels.attention(ctx, q, att, nh, kc, vc, group.page_table, group.page_size, self.window)
+            self.o.add_into(att, residual)
+            return
         qkv = self.qkv(h)
         norm = kernels.FLAG_NORM if self.qk_norm else 0
         store = kernels.FLAG_CACHE if writes_cache else 0

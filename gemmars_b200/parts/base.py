@@ -76,6 +76,7 @@ class StepContext:
     max_total: int                     # longest sequence after this step (host upper bound)
     cache: object                      # the SequenceCache
     page_size: int
+    #: what parts keep for the length of one run of the model over this context; emptied when a run starts
     extras: dict = dataclasses.field(default_factory=dict)
     pad_slot: Optional[int] = None     # slot of rows that belong to no sequence (a padded captured step)
     #: the batch's shape on the host, for steps that are not captured (None in a captured step):

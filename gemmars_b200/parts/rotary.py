@@ -38,6 +38,15 @@ class Rotary(Part):
     def kernel_units(self):
         return [("elementwise", ())]
 
+    def table(self, ctx) -> torch.Tensor:
+        """(cos, sin) of the step's packed tokens' angles, [tokens, rotary_dim / 2, 2] float32,
+        computed once a step and shared by every layer with the same rotation."""
+        key = ("rope_table", self.rotary_dim, self.theta)
+        t = ctx.extras.get(key)
+        if t is None:
+            t = ctx.extras[key] = kernels.rope_table(ctx.tok_pos, self.inv_freq(ctx.device))
+        return t
+
     def apply(self, ctx, q, k):
         """Rotates q [T, nh, hd] and k [T, nkv, hd] (contiguous views) in place."""
         for x in (q, k):

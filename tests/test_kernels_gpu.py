@@ -523,3 +523,57 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_leaves_the_context_usable(
     assert (good.float() - ref).abs().max().item() <= 2 ** -8 * ref.abs().max().item()
     assert not torch.equal(good, out)           # the launch that gave up did not finish its product
     assert k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("nh,nkv,kk,bias,norm,rope,lengths,starts", [
+    (4, 2, 512, False, True, True, [300], [0]),                       # one prompt, aligned: the fast value stores
+    (3, 1, 256, True, True, True, [70, 1, 33, 150], [0, 5, 64, 37]),     # packed, unaligned, continuing sequences
+    (2, 2, 1024, True, False, True, [129], [1000]),                    # no norm; a continuation at an odd place
+    (2, 1, 512, False, True, False, [65, 65], [0, 31]),                # no rotation
+    (5, 0, 512, True, True, True, [200], [3]),                         # queries only (a layer that reads another's cache)
+])
+def test_gemm_qkv_prompt_against_product_then_head_kernel(k, nh, nkv, kk, bias, norm, rope, lengths, starts):
+    """The q/k/v product of a prompt step with norm, rotation, scale and cache write in its epilogue,
+    against the plain product followed by the per-head kernel: the queries and the whole cache
+    (so that nothing strays), for packed sequences that start at odd places, cross pages, and end
+    in the middle of a tile."""
+    torch.manual_seed(nh + kk)
+    hd, n = 128, (nh + 2 * nkv) * 128
+    m = sum(lengths)
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
+    b = (torch.randn(n, device="cuda") * 0.1) if bias else None
+    qw = (torch.rand(hd, device="cuda") + 0.5) if norm else None
+    kw = (torch.rand(hd, device="cuda") + 0.5) if norm else None
+    inv = (1.0 / (1e4 ** (torch.arange(64, dtype=torch.float64) / 64.0))).float().cuda() if rope else None
+    eps, scale = 1e-6, hd ** -0.5
+    tok_pos = torch.tensor([s + i for s, l in zip(starts, lengths) for i in range(l)], dtype=torch.int32, device="cuda")
+    tok_seq = torch.tensor([q for q, l in enumerate(lengths) for _ in range(l)], dtype=torch.int32, device="cuda")
+    slots = torch.arange(len(lengths), dtype=torch.int32, device="cuda")
+    width = max(-(-(s + l) // 64) for s, l in zip(starts, lengths))
+    pages = len(lengths) * width
+    table = (torch.randperm(pages, generator=torch.Generator().manual_seed(1)) + 1).to(torch.int32).view(len(lengths), width).cuda()
+    caches = []
+    for fused in (False, True):
+        kc = torch.zeros((pages + 1, max(nkv, 1), 64, hd), device="cuda", dtype=torch.bfloat16)
+        vc = torch.zeros((pages + 1, max(nkv, 1), hd, 64), device="cuda", dtype=torch.bfloat16)
+        if fused:
+            q = torch.full((m, nh * hd), 9.0, device="cuda", dtype=torch.bfloat16)
+            k.gemm_qkv_prompt(x, w, b, q, nh, nkv, hd, qw, kw, eps, k.rope_table(tok_pos, inv) if rope else None, scale,
+                              tok_pos, tok_seq, slots, table if nkv else None, 64, kc if nkv else None, vc if nkv else None)
+        else:
+            qkv = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+            k.gemm(x, w, qkv, b)
+            flags = (k.FLAG_NORM if norm else 0) | (k.FLAG_ROPE if rope else 0) | (k.FLAG_CACHE if nkv else 0) | k.FLAG_INPLACE
+            k.head_norm_rope_cache(qkv, nh, nkv, hd, hd if rope else 0, qw, kw, eps, inv, scale, tok_pos, tok_seq, slots,
+                                   table if nkv else None, 64, kc if nkv else None, vc if nkv else None, flags)
+            q = qkv[:, :nh * hd]
+        caches.append((q.float().clone(), kc.float().clone(), vc.float().clone()))
+    (q0, k0, v0), (q1, k1, v1) = caches
+    # the unfused path rounds the product to bfloat16 before the per-head work, the fused one does not
+    for a, c, what in ((q0, q1, "queries"), (k0, k1, "keys"), (v0, v1, "values")):
+        tol = 2 ** -6 * max(1.0, a.abs().max().item())
+        assert (a - c).abs().max().item() <= tol, what
+    assert float(k1[0].abs().sum()) == 0.0 and float(v1[0].abs().sum()) == 0.0          # nothing strays into page 0
+    assert torch.equal(k0 != 0, k1 != 0) or (k0 - k1).abs().max().item() <= 2 ** -6      # the same places are written
+    assert k.gemm_tc_status() == 0
