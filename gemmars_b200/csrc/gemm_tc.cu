@@ -59,6 +59,7 @@ struct QkvTail {
   float eps, q_scale;
   int nh, nkv, table_width, page_size;
   const float2* rope_table; // prompts: [tokens][64] (cos, sin) of each packed token's angles, or null
+  const int2* token_place;  // prompts: [tokens] (page, position in the page) of each packed token
 };
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
 
@@ -270,6 +271,11 @@ __device__ __forceinline__ float lanes_sum_32(float (&v)[32], int lane) {
   return v[0];
 }
 
+__device__ __forceinline__ uint32_t pack_two_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *(const uint32_t*)&v;
+}
+
 // Shared memory of the prompt tail: the epilogue warps' exchange (the other half of a rotation
 // pair lives 64 features away, in warp w ^ 2; value tiles are transposed through the same memory)
 // and the warps' partial sums of squares.
@@ -285,22 +291,29 @@ __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[3
                                                  int M, int Nq, const PromptTailShared& sh, TileOut<MODE, SLOT>& tile_out) {
   const int f = warp * 32 + lane;
   const bool is_q = head < tl.nh, is_k = !is_q && head < tl.nh + tl.nkv;
-  // where this lane's token (m_first + lane) lives in the cache: its row of positions
+  // Asked for first, used last: where this lane's token (m_first + lane) lives in the cache, and
+  // the angles of the round's 32 tokens for this lane's dim.  Both are tables made once a step
+  // from the step's inputs, so nothing here waits on a chain of lookups.
   int cache_row = 0, pos_in_page = 0;
   if (!is_q) {
-    const int m = min(m_first + lane, M - 1);
-    const int pos = tl.tok_pos[m], slot = tl.seq_slot[tl.tok_seq[m]];
-    const int page = tl.page_table[(size_t)slot * tl.table_width + (pos / tl.page_size) % tl.table_width];
-    pos_in_page = pos % tl.page_size;
-    cache_row = page * tl.nkv + (head - tl.nh - (is_k ? 0 : tl.nkv));
+    const int2 place = tl.token_place[min(m_first + lane, M - 1)];
+    pos_in_page = place.y;
+    cache_row = place.x * tl.nkv + (head - tl.nh - (is_k ? 0 : tl.nkv));
+  }
+  float2 cs[32];
+  if (tl.rope_table && (is_q || is_k)) {
+    const float2* tab = tl.rope_table + (f & 63);
+#pragma unroll
+    for (int j = 0; j < 32; ++j) cs[j] = tab[(size_t)min(m_first + j, M - 1) * 64];
   }
   if (!is_q && !is_k) {
     // ---- a value head: as it is, transposed into the page ([dim][position]).  Through shared
-    // memory, so that a store covers 8 positions of one dim (16 bytes) where the 32 tokens are
-    // consecutive positions of one page that start on a multiple of 8.
-    bf16* mine = (bf16*)(sh.exchange + warp * 32 * 32);      // [32 features][32 tokens]
+    // memory (two tokens to a word, rows 17 words apart: no two lanes in one bank), so that a
+    // store covers 8 positions of one dim (16 bytes) where the 32 tokens are consecutive positions
+    // of one page that start on a multiple of 8.
+    uint32_t* mine = (uint32_t*)(sh.exchange + warp * 32 * 32);      // [32 features][17]
 #pragma unroll
-    for (int j = 0; j < 32; ++j) mine[lane * 32 + j] = __float2bfloat16_rn(x[j]);
+    for (int j = 0; j < 16; ++j) mine[lane * 17 + j] = pack_two_bf16(x[2 * j], x[2 * j + 1]);
     __syncwarp();
     const int row0 = __shfl_sync(0xffffffffu, cache_row, 0), p0 = __shfl_sync(0xffffffffu, pos_in_page, 0);
     const bool run = __all_sync(0xffffffffu, cache_row == row0 && pos_in_page == p0 + lane) && (p0 & 7) == 0 &&
@@ -310,13 +323,15 @@ __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[3
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int ff = 8 * i + fl;
-        const uint4 v = *(const uint4*)(mine + ff * 32 + 8 * ch);
+        const uint32_t* src = mine + ff * 17 + 4 * ch;
+        const uint4 v = make_uint4(src[0], src[1], src[2], src[3]);
         *(uint4*)(tl.vcache + ((size_t)row0 * BM + warp * 32 + ff) * tl.page_size + p0 + 8 * ch) = v;
       }
     } else {
+      const bf16* mine16 = (const bf16*)mine;
       for (int j = 0; j < 32; ++j) {
         const int row = __shfl_sync(0xffffffffu, cache_row, j), pp = __shfl_sync(0xffffffffu, pos_in_page, j);
-        if (m_first + j < M) tl.vcache[((size_t)row * BM + f) * tl.page_size + pp] = mine[lane * 32 + j];
+        if (m_first + j < M) tl.vcache[((size_t)row * BM + f) * tl.page_size + pp] = mine16[lane * 34 + j];
       }
     }
     __syncwarp();
@@ -342,12 +357,10 @@ __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[3
 #pragma unroll
     for (int j = 0; j < 32; ++j) mine[j * 32 + lane] = x[j];
     asm volatile("bar.sync 1, 128;" ::: "memory");
-    const float2* tab = tl.rope_table + (f & 63);
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
-      const float2 cs = tab[(size_t)min(m_first + j, M - 1) * 64];
       const float other = theirs[j * 32 + lane];
-      x[j] = f < 64 ? x[j] * cs.x - other * cs.y : x[j] * cs.x + other * cs.y;
+      x[j] = f < 64 ? x[j] * cs[j].x - other * cs[j].y : x[j] * cs[j].x + other * cs[j].y;
     }
   }
   if (is_q) {
@@ -869,6 +882,19 @@ __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* 
   table[i] = make_float2(c, s);
 }
 
+// Where every packed token lives in a group's cache: place[t] = (page, position in the page), once
+// per step for all the layers that share the group's page table.
+__global__ void token_place_kernel(const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                                   const int* __restrict__ seq_slot, const int* __restrict__ page_table, int table_width,
+                                   int page_size, int2* __restrict__ place, int ntok) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= ntok) return;
+  const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
+  place[t] = make_int2(page_table[(size_t)slot * table_width + (pos / page_size) % table_width], pos % page_size);
+}
+
 // ------------------------------------------------------------------ host side
 
 // The result's tensor map, and whether TMA can address the result at all.
@@ -1075,21 +1101,31 @@ GB_EXPORT int gb_rope_table(const int* tok_pos, const float* inv_freq, void* tab
   return gb_launch_status();
 }
 
+// (page, position in the page) of every packed token: place [ntok] int2, for gb_gemm_tc_qkv_prompt.
+GB_EXPORT int gb_token_place(const int* tok_pos, const int* tok_seq, const int* seq_slot, const int* page_table,
+                             int table_width, int page_size, void* place, int ntok, cudaStream_t stream) {
+  if (ntok <= 0) return 0;
+  if (!tok_pos || !tok_seq || !seq_slot || !page_table || !place || page_size <= 0 || table_width <= 0) return GB_ERR_ARG;
+  gb_launch(token_place_kernel, dim3((ntok + 255) / 256), dim3(256), 0, stream, tok_pos, tok_seq, seq_slot, page_table,
+            table_width, page_size, (int2*)place, ntok);
+  return gb_launch_status();
+}
+
 // The q/k/v product of a prompt step (more than 64 tokens) with the per-head work in its epilogue
 // (head size 128): y [M, nh * 128] (rows ldy apart) gets the queries, normed, rotated and scaled;
-// the keys (normed, rotated) and the values go straight into the paged cache, which must be
-// given.  q_weight / k_weight null: no norm; rope_table ([M][64] (cos, sin), see gb_rope_table)
-// null: no rotation.  ctas: CTAs to launch.
+// the keys (normed, rotated) and the values go straight into the paged cache, at the places
+// token_place ([M] (page, position in the page), see gb_token_place) names.  q_weight / k_weight
+// null: no norm; rope_table ([M][64] (cos, sin), see gb_rope_table) null: no rotation.  ctas: CTAs
+// to launch.
 GB_EXPORT int gb_gemm_tc_qkv_prompt(const void* x, const void* w, const float* bias, void* y, int M, int N, int K,
                                     long long ldx, long long ldy, int ctas, const float* q_weight, const float* k_weight,
-                                    const void* rope_table, float eps, float q_scale, int nh, int nkv, const int* tok_pos,
-                                    const int* tok_seq, const int* seq_slot, const int* page_table, int table_width,
-                                    int page_size, void* kcache, void* vcache, cudaStream_t stream) {
+                                    const void* rope_table, float eps, float q_scale, int nh, int nkv,
+                                    const void* token_place, int page_size, void* kcache, void* vcache,
+                                    cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return GB_ERR_SIZE;
-  if (nh <= 0 || nkv < 0 || N != (nh + 2 * nkv) * BM || !tok_pos) return GB_ERR_SIZE;
-  if (nkv > 0 && (!tok_seq || !seq_slot || !page_table || !kcache || !vcache || page_size <= 0 || (page_size % 8)))
-    return GB_ERR_ARG;
+  if (nh <= 0 || nkv < 0 || N != (nh + 2 * nkv) * BM) return GB_ERR_SIZE;
+  if (nkv > 0 && (!token_place || !kcache || !vcache || page_size <= 0 || (page_size % 8))) return GB_ERR_ARG;
   if ((q_weight == nullptr) != (k_weight == nullptr)) return GB_ERR_ARG;
   if ((ldy % 8) || ((uintptr_t)y & 15)) return GB_ERR_SIZE;    // the queries leave by TMA
   const int bn = M <= 128 ? 128 : 256;
@@ -1098,8 +1134,8 @@ GB_EXPORT int gb_gemm_tc_qkv_prompt(const void* x, const void* w, const float* b
   if (!tensor_map(&mx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx * 2, (uint32_t)bn)) return GB_ERR_ARG;
   const OutMap my = out_map(y, EPI_STORE_BF16, M, nh * BM, ldy, 32);
   if (!my.usable) return GB_ERR_ARG;
-  QkvTail tail{q_weight, k_weight, nullptr, tok_pos, tok_seq, seq_slot, page_table, (bf16*)kcache, (bf16*)vcache,
-               eps, q_scale, nh, nkv, table_width, page_size, (const float2*)rope_table};
+  QkvTail tail{q_weight, k_weight, nullptr, nullptr, nullptr, nullptr, nullptr, (bf16*)kcache, (bf16*)vcache,
+               eps, q_scale, nh, nkv, 1, page_size, (const float2*)rope_table, (const int2*)token_place};
   if (bn > 128) return launch_persistent<256, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
   return launch_persistent<128, 6, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
 }

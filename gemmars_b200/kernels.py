@@ -371,8 +371,11 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == n
     if bn is None:
-        # 256 tokens a tile; narrower tiles that fill the last round better (240 tokens for 2,048 x 4,096)
-        # were 1.5 % faster alone and 4 % slower inside a prompt step
+        # 256 tokens a tile.  Narrower tiles that fill the last round of tiles better were measured and
+        # are slower: 240 tokens for 2,048 x 4,096 (1.5 % faster alone, 4 % slower inside a prompt step),
+        # and 128 tokens where 256 leave the last round nearly empty (2,048 x 2,560 is 160 tiles on 148
+        # SMs; a 2,048-token prompt of a 4B-shaped model took 20.5 ms against 18.4, of a 32B-shaped one
+        # 35.3 ms against 30.9 over 16 layers)
         bn = 128 if m <= 128 else 256
     f = _fn("gemm_tc", "gb_gemm_tc_persistent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
@@ -441,6 +444,18 @@ def rope_table(tok_pos, inv_freq):
     return table
 
 
+def token_place(tok_pos, tok_seq, seq_slot, page_table, page_size):
+    """int32 [tokens, 2]: (page, position in the page) of every packed token of a step in the cache
+    that ``page_table`` describes; made once a step for all the layers that share the table."""
+    _cuda(tok_pos, tok_seq, seq_slot, page_table)
+    ntok = tok_pos.numel()
+    place = torch.empty((ntok, 2), dtype=torch.int32, device=tok_pos.device)
+    f = _fn("gemm_tc", "gb_token_place", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(f(tok_pos.data_ptr(), tok_seq.data_ptr(), seq_slot.data_ptr(), page_table.data_ptr(), page_table.shape[1],
+             page_size, place.data_ptr(), ntok, _stream()), "token_place", "elementwise", _nbytes(place))
+    return place
+
+
 def gemm_qkv_prompt_usable(x, w, nh: int, nkv: int, hd: int, rot: int, page_size: int) -> bool:
     """Whether the q/k/v product of a prompt step can do the per-head work in its epilogue:
     bfloat16, more than 64 tokens, heads of 128 rotated over all dims or not at all."""
@@ -448,13 +463,14 @@ def gemm_qkv_prompt_usable(x, w, nh: int, nkv: int, hd: int, rot: int, page_size
             and w.shape[0] == (nh + 2 * nkv) * hd and gemm_tc_usable(x, w))
 
 
-def gemm_qkv_prompt(x, w, bias, q_out, nh, nkv, hd, q_weight, k_weight, eps, table, q_scale, tok_pos, tok_seq, seq_slot,
-                    page_table, page_size, kcache, vcache, ctas=None):
+def gemm_qkv_prompt(x, w, bias, q_out, nh, nkv, hd, q_weight, k_weight, eps, table, q_scale, place, page_size, kcache,
+                    vcache, ctas=None):
     """q_out[:, :nh*hd] = a prompt step's queries, normed per head, rotated and scaled; the keys
     (normed, rotated) and the values go into the paged cache: the q/k/v product of more than 64
     tokens and head_norm_rope_cache in one kernel.  ``table``: rope_table of the step's tokens
-    (None: no rotation).  See gemm_qkv_prompt_usable."""
-    _cuda(x, w, bias, q_out, q_weight, k_weight, table, tok_pos, tok_seq, seq_slot, page_table, kcache, vcache)
+    (None: no rotation); ``place``: token_place of the step's tokens in this cache (None with no
+    kv heads).  See gemm_qkv_prompt_usable."""
+    _cuda(x, w, bias, q_out, q_weight, k_weight, table, place, kcache, vcache)
     m, k = x.shape
     n = w.shape[0]
     assert q_out.dtype == torch.bfloat16 and q_out.shape == (m, nh * hd) and q_out.stride(1) == 1 and w.is_contiguous()
@@ -463,18 +479,17 @@ def gemm_qkv_prompt(x, w, bias, q_out, nh, nkv, hd, q_weight, k_weight, eps, tab
     if nkv:
         assert kcache.dtype == torch.bfloat16 and kcache.is_contiguous() and kcache.shape[1:] == (nkv, page_size, hd)
         assert vcache.is_contiguous() and vcache.shape[1:] == (nkv, hd, page_size)
+        assert place.dtype == torch.int32 and place.shape == (m, 2) and place.is_contiguous()
     if table is not None:
         assert table.dtype == torch.float32 and table.shape == (m, hd // 2, 2) and table.is_contiguous()
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == n
     f = _fn("gemm_tc", "gb_gemm_tc_qkv_prompt",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
-             c_void_p, c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
-             c_void_p, c_void_p])
+             c_void_p, c_float, c_float, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), q_out.data_ptr(), m, n, k, x.stride(0), q_out.stride(0),
              ctas or sm_count(x.device), _ptr(q_weight), _ptr(k_weight), _ptr(table), eps, q_scale, nh, nkv,
-             tok_pos.data_ptr(), _ptr(tok_seq), _ptr(seq_slot), _ptr(page_table),
-             page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache), _ptr(vcache), _stream()),
+             _ptr(place) if nkv else None, page_size, _ptr(kcache), _ptr(vcache), _stream()),
            "gemm_qkv_prompt", "matmul", _nbytes(x, w, bias, q_out) + m * 2 * nkv * hd * 2)
 
 

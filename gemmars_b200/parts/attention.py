@@ -93,6 +93,17 @@ class Attention(Part):
         return self.compute == "bfloat16" and not kernels.attention_decode_stream_usable(
             1, self.num_heads, self.num_kv_heads, self.head_dim, PAGE_SIZE)
 
+    @staticmethod
+    def _token_place(ctx, group):
+        """(page, position in the page) of the step's tokens in ``group``'s cache, made once a step
+        for all the layers of the group."""
+        key = ("token_place", id(group))
+        t = ctx.extras.get(key)
+        if t is None:
+            t = ctx.extras[key] = kernels.token_place(ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, group.page_table,
+                                                      group.page_size)
+        return t
+
     # ---- step
     def forward(self, ctx, h, residual, caches, writes_cache=True):
         nh, hd = self.num_heads, self.head_dim
@@ -121,8 +132,8 @@ class Attention(Part):
             q = torch.empty((h.shape[0], nh * hd), dtype=h.dtype, device=h.device)
             kernels.gemm_qkv_prompt(h, self.qkv.weight, self.qkv.bias, q, nh, nkv, hd,
                                     self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None,
-                                    self.eps, self.position.table(ctx) if rot else None, self.scale, ctx.tok_pos,
-                                    ctx.tok_seq, ctx.seq_slot, group.page_table if nkv else None, group.page_size,
+                                    self.eps, self.position.table(ctx) if rot else None, self.scale,
+                                    self._token_place(ctx, group) if nkv else None, group.page_size,
                                     kc if nkv else None, vc if nkv else None)
             att = torch.empty_like(q)
             kernels.attention(ctx, q, att, nh, kc, vc, group.page_table, group.page_size, self.window)

@@ -559,8 +559,9 @@ def test_gemm_qkv_prompt_against_product_then_head_kernel(k, nh, nkv, kk, bias, 
         vc = torch.zeros((pages + 1, max(nkv, 1), hd, 64), device="cuda", dtype=torch.bfloat16)
         if fused:
             q = torch.full((m, nh * hd), 9.0, device="cuda", dtype=torch.bfloat16)
+            place = k.token_place(tok_pos, tok_seq, slots, table, 64) if nkv else None
             k.gemm_qkv_prompt(x, w, b, q, nh, nkv, hd, qw, kw, eps, k.rope_table(tok_pos, inv) if rope else None, scale,
-                              tok_pos, tok_seq, slots, table if nkv else None, 64, kc if nkv else None, vc if nkv else None)
+                              place, 64, kc if nkv else None, vc if nkv else None)
         else:
             qkv = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
             k.gemm(x, w, qkv, b)
