@@ -35,19 +35,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
 
-def _qwen3(layers, hidden, heads, kv_heads, inter, tied):
-    return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": layers,
-            "hidden_size": hidden, "num_attention_heads": heads, "num_key_value_heads": kv_heads, "head_dim": 128,
-            "intermediate_size": inter, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
-            "attention_bias": False, "tie_word_embeddings": tied, "max_position_embeddings": 40960}
+from gemmars_b200.tuning import SHAPES as CONFIGS, random_engine, synthetic_fill   # noqa: E402  (the layer sizes measured at)
 
-
-# The layer sizes of the benchmark configurations (Qwen3-8B is the headline one).
-CONFIGS = {
-    "8b": ("Qwen3-8B shape", _qwen3(36, 4096, 32, 8, 12288, False)),
-    "4b": ("Qwen3-4B shape", _qwen3(36, 2560, 32, 8, 9728, True)),
-    "32b": ("Qwen3-32B shape", _qwen3(64, 5120, 64, 8, 25600, False)),
-}
 CONTEXT = 8192
 PREFILL_TOKENS = 2048
 E2E_TOKENS = 256
@@ -144,13 +133,7 @@ def fill_cache(runner, slots, length, real, vocab, gen):
             toks = torch.randint(0, vocab, (length,), generator=gen).tolist()
             runner.step([StepItem(s, toks, [])])
         return
-    for s in slots:
-        runner.cache.extend(s, length)
-    runner.cache.sync()
-    for g in runner.cache.kv_groups:
-        for t in (g.k, g.v):
-            for layer in range(t.shape[0]):
-                t[layer].normal_(0.0, 1.0)
+    synthetic_fill(runner, slots, length)
 
 
 def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs):
@@ -224,18 +207,7 @@ def time_prefill(eng, cfg, tokens, tflops, tflops_sustained):
 
 
 def make_engine(cfg, max_batch, cache_tokens, options=""):
-    import torch
-    from gemmars_b200.engine.engine import Engine, EngineOptions
-    from gemmars_b200.weights.random_init import random_weights
-    torch.cuda.set_device(0)
-    tensors = random_weights(cfg, seed=0, device="cuda:0")
-    opts = EngineOptions.parse({"dtype": "bfloat16", "max_batch": str(max_batch), "max_tokens": str(cache_tokens),
-                                "prefill_chunk": "2048"})
-    for pair in filter(None, (p.strip() for p in options.split(";"))):
-        opts.set(*[x.strip() for x in pair.split("=", 1)])
-    # the engine takes the tensors out of the dict as it binds them, so that a model of 65 GB and
-    # its stacked q/k/v and gate/up copies never sit in memory side by side
-    return Engine.from_config(cfg, tensors, opts, consume=True)
+    return random_engine(cfg, max_batch, cache_tokens, options)
 
 
 def config_record(name, cfg, layers_full, batch, context, fill, peak_line):
@@ -263,7 +235,7 @@ def run_8b(args, name, cfg, layers_full):
 
     # end to end through the entry point: host ids in, host ids out, 256 tokens a sequence
     gen = torch.Generator().manual_seed(2)
-    e2e_new = max(E2E_TOKENS, args.steps + 1)
+    e2e_new = max(2, args.e2e_tokens)
     prompts = [torch.randint(0, vocab, (args.context - e2e_new,), generator=gen).tolist() for _ in range(args.batch)]
     clocks = ClockSampler().start()
     res = eng.generate(prompts, max_tokens=e2e_new, stop_ids=[])
@@ -386,6 +358,8 @@ def main():
     ap.add_argument("--fill", choices=["real", "synthetic"], default="real",
                     help="how the cache is brought to the context length before decoding is timed")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--e2e-tokens", type=int, default=E2E_TOKENS,
+                    help="tokens a sequence generates in the end-to-end run (fewer for runs under a profiler)")
     ap.add_argument("--options", default="", help='further engine options, "key=value;key=value"')
     args = ap.parse_args()
     if args.impl == "reference":

@@ -221,6 +221,57 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_merge_kernel(
   }
 }
 
+// ------------------------------------------------------------------ all rows greedy
+// The first maximum of every row, without any selection: a slice's largest value by a plain
+// reduction (the value's order is "larger logit first, then smaller token id"), then the largest of
+// the slices' results.
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+
+constexpr int ARGMAX_THREADS = 256;
+
+__global__ void __launch_bounds__(ARGMAX_THREADS) argmax_slice_kernel(const float* __restrict__ logits, long long stride, int vocab,
+                                                                     int slice_len, unsigned long long* __restrict__ cand) {
+  __shared__ unsigned long long warp_best[ARGMAX_THREADS / 32];
+  pdl_release_next();
+  pdl_wait_prior();
+  const int slice = blockIdx.x, row = blockIdx.y, tid = threadIdx.x;
+  const int lo = slice * slice_len, hi = min(vocab, lo + slice_len);
+  const float* l = logits + (size_t)row * stride;
+  unsigned long long best = 0ull;
+  for (int i = lo + tid; i < hi; i += ARGMAX_THREADS) {
+    const unsigned long long c = candidate(l[i], i);
+    best = c > best ? c : best;
+  }
+  best = warp_max_u64(best);
+  if ((tid & 31) == 0) warp_best[tid >> 5] = best;
+  __syncthreads();
+  if (tid < 32) {
+    best = warp_max_u64(tid < ARGMAX_THREADS / 32 ? warp_best[tid] : 0ull);
+    if (tid == 0) cand[(size_t)row * gridDim.x + slice] = best;
+  }
+}
+
+__global__ void __launch_bounds__(32) argmax_merge_kernel(const unsigned long long* __restrict__ cand, int slices,
+                                                          int* __restrict__ out) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int row = blockIdx.x;
+  unsigned long long best = 0ull;
+  for (int i = threadIdx.x; i < slices; i += 32) {
+    const unsigned long long c = cand[(size_t)row * slices + i];
+    best = c > best ? c : best;
+  }
+  best = warp_max_u64(best);
+  if (threadIdx.x == 0) out[row] = best ? candidate_token(best) : 0;
+}
+
 // ------------------------------------------------------------------ more than 1,024 candidates
 // top_k = 0 (every token is a candidate, src/sampler.rs:43-47) or top_k > 1,024: the candidates do
 // not fit shared memory, so the row's tokens are sorted in global scratch: a stable radix sort by
@@ -366,6 +417,11 @@ GB_EXPORT int gb_sample(const float* logits, long long stride, int rows, int voc
   if (slices == 0) return GB_ERR_SIZE;
   unsigned long long* cand = (unsigned long long*)scratch;
   int* counts = (int*)(cand + (size_t)rows * slices * cap);
+  if (!temperature) {   // every row takes its first maximum
+    gb_launch(argmax_slice_kernel, dim3(slices, rows), ARGMAX_THREADS, 0, stream, logits, stride, vocab, slice_len, cand);
+    gb_launch(argmax_merge_kernel, rows, 32, 0, stream, (const unsigned long long*)cand, slices, out);
+    return gb_launch_status();
+  }
   gb_launch(sample_slice_kernel, dim3(slices, rows), SAMPLE_THREADS, 0, stream, logits, stride, vocab, slice_len,
             temperature, top_k, cand, counts, cap);
   gb_launch(sample_merge_kernel, rows, SAMPLE_THREADS, 0, stream, logits, stride, vocab, slices, temperature, top_k, top_p,

@@ -131,3 +131,14 @@ def test_schedule_validation():
     plan.schedule = [ScheduleEntry(5)]
     with pytest.raises(ValueError):
         plan.validate()
+
+
+def test_measurement_shapes_are_configurations():
+    """The layer sizes the measurements are taken at read as configurations of the architecture."""
+    from gemmars_b200.tuning import SHAPES, main
+    for name, (label, raw) in SHAPES.items():
+        cfg = Qwen3Config.from_dict(raw)
+        assert cfg.dim_per_head == 128 and label.startswith("Qwen3-")
+    assert SHAPES["4b"][1]["tie_word_embeddings"] and not SHAPES["32b"][1]["tie_word_embeddings"]
+    with pytest.raises(SystemExit):
+        main(["no-such-command"])
