@@ -253,3 +253,32 @@ def test_float32_at_released_layer_sizes_against_the_plain_implementation():
             pos[i] += 1
     for i in range(3):
         assert np.array_equal(np.stack(got[i]), whole[i]), f"request {i} depends on the batch"
+
+
+def test_the_ring_wraps_under_the_fused_prompt_product(tmp_path_factory):
+    """Heads of 128, bfloat16, a window of 40 on one layer, prompts cut into chunks of 128 tokens:
+    the q/k/v product writes keys and values into the cache from its epilogue, through a ring of
+    4 pages that a sequence of 600 tokens goes round more than twice; then single tokens."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    from gemmars_b200.weights import write_random_model
+    cfg = dict(SMALL_128, sliding_window=40)
+    folder = str(tmp_path_factory.mktemp("ring128"))
+    write_random_model(folder, cfg, seed=12)
+    pcfg, w = plain.load_folder(folder)
+    toks = np.random.default_rng(4).integers(0, cfg["vocab_size"], 640).tolist()
+    ref = plain.forward(pcfg, w, toks)
+    scale = float(np.abs(ref).max())
+    model = build_model(folder, dtype="bfloat16")
+    r = Runner(model, max_tokens=64 * 24, max_batch=2, prefill_chunk=128, max_step_tokens=256)
+    assert [g.table_width for g in r.cache.kv_groups if g.need.window is not None] == [4]
+    slot, other = r.open(), r.open()
+    # two sequences side by side, so that a sub-step packs 128 tokens of each (one starts at an odd place)
+    r.step([StepItem(other, toks[:37], [])])
+    out = r.step([StepItem(slot, toks[:600], range(600)), StepItem(other, toks[37:300], [262])]).float().cpu().numpy()
+    err = np.abs(out[:600] - ref[:600]).max(axis=1)
+    p = int(err.argmax())
+    assert err[p] <= TOL_BF16["S128"] * scale, f"position {p} is off by {err[p]:.3e} (scale {scale:.2f})"
+    assert np.abs(out[600] - ref[299]).max() <= TOL_BF16["S128"] * scale
+    for i in range(600, 640):
+        row = r.step([StepItem(slot, [toks[i]], [0])])[0].float().cpu().numpy()
+        assert np.abs(row - ref[i]).max() <= TOL_BF16["S128"] * scale, i
