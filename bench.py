@@ -152,20 +152,30 @@ def time_decode(eng, batch, ctx_end, steps, warmup, real_fill, hbm_gbs):
     sampler = BatchSampler([SamplingParams()] * batch, runner.device)
     toks = torch.randint(0, vocab, (batch,), generator=gen).tolist()
 
-    def one(toks):
-        logits = runner.step([StepItem(s, [t], [0]) for s, t in zip(slots, toks)])
-        return sampler.sample_device(logits, list(range(batch)))
+    rows = list(range(batch))
+    ahead = eng.options.decode_ahead and runner.use_graphs
 
-    for _ in range(warmup):
-        toks = one(toks).tolist()
+    def one(logits):
+        """A step as the generation loop runs it: draw from the logits, launch the next step from
+        the drawn tokens where they lie, then read them on the host (what generation needs them
+        for: stop tokens, limits, the caller)."""
+        drawn = sampler.draw(logits, rows)
+        nxt = runner.decode_from_device(slots, drawn) if ahead else None
+        toks = sampler.read(drawn)
+        if nxt is None:
+            nxt = runner.step([StepItem(s, [t], [0]) for s, t in zip(slots, toks)])
+        return nxt
+
+    logits = runner.step([StepItem(s, [t], [0]) for s, t in zip(slots, toks)])
+    for _ in range(warmup - 1):
+        logits = one(logits)
     torch.cuda.synchronize()
     clocks = ClockSampler().start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches0 = kernels.launch_count()
-    cur = toks
     e0.record()
     for _ in range(steps):
-        cur = one(cur).tolist()          # the next step's tokens come back to the host, as in generation
+        logits = one(logits)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps

@@ -52,9 +52,11 @@ class EngineOptions:
     max_batch: int = 64                  # most sequences generating together
     max_tokens: Optional[int] = None     # tokens the cache holds over all sequences
     cuda_graphs: bool = True             # replay decode steps from captured graphs
+    decode_ahead: bool = True            # launch the next decode step before the host has read this step's tokens
     profile: bool = False
 
-    KEYS = ("dtype", "device", "prefill_chunk", "max_context", "max_batch", "max_tokens", "cuda_graphs", "profile")
+    KEYS = ("dtype", "device", "prefill_chunk", "max_context", "max_batch", "max_tokens", "cuda_graphs", "decode_ahead",
+            "profile")
 
     def set(self, key: str, value: str) -> None:
         """Sets an option by name; unknown keys are errors (src/engine.rs:276-329)."""
@@ -71,7 +73,7 @@ class EngineOptions:
             setattr(self, key, _parse_opt_int(key, value))
         elif key == "max_batch":
             self.max_batch = _parse_opt_int(key, value) or 1
-        elif key in ("cuda_graphs", "profile"):
+        elif key in ("cuda_graphs", "decode_ahead", "profile"):
             setattr(self, key, _parse_bool(key, value))
         else:
             raise ValueError(f"unknown option {key!r} (known: {', '.join(self.KEYS)})")
@@ -180,7 +182,8 @@ class Engine:
         # a batch is as large as the free slots allow: the conversation of ``send`` holds one
         return GenerationLoop(r.open, r.close, step, make_sampler,
                               max(1, min(self.options.max_batch, r.cache.slots.free_count)),
-                              r.cache.n_pages - r.cache.pages_held(), r.cache.page_size, self.max_context)
+                              r.cache.n_pages - r.cache.pages_held(), r.cache.page_size, self.max_context,
+                              step_ahead=r.decode_from_device if self.options.decode_ahead else None)
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: Optional[int] = None,
                  sampling: Optional[SamplingParams] = None, stop_ids: Optional[Sequence[int]] = None,

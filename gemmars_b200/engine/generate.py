@@ -78,8 +78,15 @@ class GenerationLoop:
     -> object with sample(logits, seq indices) -> token ids``."""
 
     def __init__(self, open_slot: Callable, close_slot: Callable, step: Callable, make_sampler: Callable,
-                 max_batch: int, cache_pages: int, page_size: int, max_context: Optional[int] = None):
+                 max_batch: int, cache_pages: int, page_size: int, max_context: Optional[int] = None,
+                 step_ahead: Optional[Callable] = None):
+        """``step_ahead(slots, drawn) -> logits rows or None`` (optional): runs one token for each
+        slot, the tokens being what the sampler's ``draw`` returned and nobody has read yet, so
+        that the next step is on its way while this one's tokens are read and judged.  With it the
+        sampler must have ``draw(logits, seq indices) -> drawn`` and ``read(drawn) -> token ids``."""
         self.open_slot, self.close_slot, self.step, self.make_sampler = open_slot, close_slot, step, make_sampler
+        self.step_ahead = step_ahead
+        self.ahead_steps = 0
         self.max_batch, self.cache_pages, self.page_size, self.max_context = max_batch, cache_pages, page_size, max_context
         self.decode_steps = 0
         self.prefill_steps = 0
@@ -139,7 +146,21 @@ class GenerationLoop:
                 if requests[i].max_tokens <= 0:     # a kept sequence: its tokens are run, nothing is drawn
                     self._finish(i, LENGTH, *fin)
             while live:
-                toks = sampler.sample(logits, [batch.index(i) for i in live])
+                rows = [batch.index(i) for i in live]
+                ahead = None
+                # (not for a sequence whose slot lives on: its last token must stay unrun, to be fed
+                # first by the turn after)
+                if self.step_ahead is not None and not kept and self._may_run_ahead(live, requests, out, held):
+                    # The next step is launched from the tokens as the sampler left them, before
+                    # anyone has read them: rows are independent, so a sequence that turns out to
+                    # have ended only wastes its row, and the others' logits are there already
+                    # when the host has judged this step's tokens.
+                    drawn = sampler.draw(logits, rows)
+                    ahead = self.step_ahead([slots[i] for i in live], drawn)
+                    toks = sampler.read(drawn)
+                else:
+                    toks = sampler.sample(logits, rows)
+                before = list(live)
                 now = time.perf_counter()
                 if first:
                     self.prefill_secs += now - t_mark
@@ -163,7 +184,13 @@ class GenerationLoop:
                         nxt.append((i, int(tok)))
                 if not nxt:
                     break
-                logits = self.step([(slots[i], [tok]) for i, tok in nxt])
+                if ahead is not None:
+                    going = {i for i, _ in nxt}
+                    keep = [k for k, i in enumerate(before) if i in going]
+                    logits = ahead if len(keep) == len(before) else ahead[keep]
+                    self.ahead_steps += 1
+                else:
+                    logits = self.step([(slots[i], [tok]) for i, tok in nxt])
                 self.decode_steps += 1
                 for i, _ in nxt:
                     forwards[i] += 1
@@ -173,6 +200,15 @@ class GenerationLoop:
                 if i not in kept:
                     self.close_slot(s)
                 del slots[i]
+
+    def _may_run_ahead(self, live, requests, out, held) -> bool:
+        """Whether the next step may be launched before this step's tokens are known: some
+        sequence must be able to go on after this token, and every sequence must still fit its
+        context with one more position (a sequence at its limit ends with this token; its row of
+        the step ahead would have nowhere to write)."""
+        if self.max_context and any(held[i] + 1 > self.max_context for i in live):
+            return False
+        return any(len(out[i]) + 1 < requests[i].max_tokens for i in live)
 
     def _finish(self, i, reason, requests, out, forwards, results, slots, live, kept):
         unfed = out[i][-1] if out[i] and reason != STOP else None

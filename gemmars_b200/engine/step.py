@@ -234,6 +234,39 @@ class Runner:
             else:
                 out[torch.tensor(dest, device=self.device)] = logits
 
+    def decode_from_device(self, slots: Sequence[int], tokens: torch.Tensor) -> Optional[torch.Tensor]:
+        """One more token for each sequence in ``slots``, the tokens being an int32 tensor on the
+        device (what the sampler has just drawn and the host has not read yet): the step is
+        launched without waiting for them, so that the device goes on while the host reads and
+        judges the tokens of the step before.  Returns float32 logits [len(slots), vocab], or None
+        when the step cannot be run this way (no captured steps, or the cache cannot take it):
+        the caller then runs an ordinary step.  A token id outside the vocabulary cannot be
+        refused here; the embedding reads the nearest row that exists."""
+        slots = [int(s) for s in slots]
+        b = len(slots)
+        if (not self.use_graphs or b == 0 or tokens.device != self.device or tokens.dtype != torch.int32
+                or tokens.numel() != b or len(set(slots)) != b):
+            return None
+        if any(s not in self.cache.lengths or s in self._broken for s in slots):
+            return None
+        if not self.cache.can_extend([(s, 1) for s in slots]):
+            return None
+        before = {s: self.cache.lengths[s] for s in slots}
+        try:
+            starts = np.fromiter((self.cache.extend(s, 1) for s in slots), dtype=np.int64, count=b)
+            self.cache.sync()
+            logits = self._decode_graph(tokens, starts, np.asarray(slots, dtype=np.int64), int(starts.max()) + 1)
+            out = torch.empty((b, self.vocab_size), dtype=torch.float32, device=self.device)
+            out.copy_(logits)
+        except BaseException:
+            for slot, old in before.items():
+                if slot in self.cache.lengths and not self.cache.rollback(slot, old):
+                    self._broken.add(slot)
+            raise
+        self.steps_run += 1
+        self.tokens_run += b
+        return out
+
     # ---- decode steps replayed from CUDA graphs
     def _decode_graph(self, tokens, starts, slots, max_total):
         """One token per sequence through a captured graph.  The batch is padded to a power of
@@ -336,7 +369,9 @@ class _DecodeGraph:
             self.events[i].synchronize()       # the copy that last read this host buffer is done
         h = self.host_np[i]
         h[:] = self.fixed
-        h[0:b] = tokens
+        on_device = isinstance(tokens, torch.Tensor)
+        if not on_device:
+            h[0:b] = tokens
         h[bp:bp + b] = starts                  # the token's position is the length before the step
         h[3 * bp:3 * bp + b] = slots
         h[4 * bp:4 * bp + b] = starts
@@ -344,6 +379,8 @@ class _DecodeGraph:
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
+        if on_device:
+            self.d_tokens[:b].copy_(tokens)    # in stream order after the block above and after the sampler
         self.graph.replay()
         kernels.count_launches(self.launches)
         return self.logits

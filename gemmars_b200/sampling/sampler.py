@@ -79,6 +79,7 @@ class BatchSampler:
         # work for a smaller bound
         self.cap = max([p.top_k for p in params if not p.greedy and not p.wide] + [1])
         self._host, self._events, self._turn = None, [None] * self.RING, 0
+        self._copy_stream, self._host_tokens, self._drawn_at = None, None, None
 
     def sample(self, logits: torch.Tensor, seqs: Sequence[int]) -> List[int]:
         """``logits``: float32 [len(seqs), vocab] on the device; ``seqs``: which sequence each
@@ -110,6 +111,33 @@ class BatchSampler:
         ev.record()
         self._events[i] = ev
         return dev_f, dev_k
+
+    def draw(self, logits: torch.Tensor, seqs: Sequence[int]) -> torch.Tensor:
+        """As ``sample``, but the tokens stay on the device (int32 [len(seqs)]) until ``read``."""
+        drawn = self.sample_device(logits, seqs)
+        if drawn.is_cuda:
+            self._drawn_at = torch.cuda.Event()
+            self._drawn_at.record()
+        return drawn
+
+    def read(self, drawn: torch.Tensor) -> List[int]:
+        """The tokens of the last ``draw`` on the host.  They are fetched on a stream of their own
+        that waits for the sampler alone: on the stream the step runs on, the copy would queue up
+        behind whatever was launched since (the next step, when it was launched ahead) and the
+        host would learn the tokens a whole step late."""
+        if not drawn.is_cuda:
+            return drawn.tolist()
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=drawn.device)
+            self._host_tokens = torch.empty(max(len(self.params), drawn.numel()), dtype=torch.int32).pin_memory()
+        n = drawn.numel()
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(self._drawn_at)
+            self._host_tokens[:n].copy_(drawn, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(self._copy_stream)
+        done.synchronize()
+        return self._host_tokens[:n].tolist()
 
     def sample_device(self, logits: torch.Tensor, seqs: Sequence[int]) -> torch.Tensor:
         n = len(seqs)

@@ -144,11 +144,16 @@ def timeline(shape, batch, context, layers, prompt, temperature, out=sys.stdout)
         slots = [runner.open() for _ in range(batch)]
         synthetic_fill(runner, slots, context - 50)
         sampler = BatchSampler([SamplingParams(temperature=temperature)] * batch, runner.device)
-        cur = [5] * batch
+        rows = list(range(batch))
+        state = {"logits": runner.step([StepItem(s, [5], [0]) for s in slots])}
 
         def step():
-            logits = runner.step([StepItem(s, [t], [0]) for s, t in zip(slots, cur)])
-            return sampler.sample_device(logits, list(range(batch))).tolist()
+            # as the generation loop steps: draw, launch the next step from the drawn tokens where
+            # they lie, then read them on the host
+            drawn = sampler.draw(state["logits"], rows)
+            nxt = runner.decode_from_device(slots, drawn) if eng.options.decode_ahead else None
+            toks = sampler.read(drawn)
+            state["logits"] = nxt if nxt is not None else runner.step([StepItem(s, [t], [0]) for s, t in zip(slots, toks)])
         what = f"decode step, batch {batch}, context {context}" + (f", temperature {temperature}" if temperature > 0 else "")
     for _ in range(5):
         step()

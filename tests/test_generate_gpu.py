@@ -41,6 +41,27 @@ def test_greedy_generation_matches_plain(cfg, model_folders):
     assert [r.tokens for r in reversed(again)] == [r.tokens for r in res]
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_launched_ahead_give_the_same_tokens(dtype, model_folders):
+    """The next decode step is launched from the sampler's tokens on the device before the host has
+    read them.  Greedy and seeded temperature generation must give exactly what the engine gives
+    when every step waits for the host, stop tokens met along the way and batches of unequal
+    lengths included; and steps must really have been launched ahead."""
+    from gemmars_b200 import Engine, SamplingParams
+    folder = model_folders(TINY_B)
+    prompts = _prompts(TINY_B, [7, 13, 1, 40, 66, 5], seed=5)
+    results = {}
+    for ahead in ("true", "false"):
+        eng = Engine.load(folder, f"dtype={dtype};max_batch=4;max_tokens=4096;decode_ahead={ahead}")
+        free_run = eng.generate(prompts[:1], max_tokens=10, stop_ids=[])[0].tokens
+        greedy = eng.generate(prompts, max_tokens=14, stop_ids=[free_run[6]])
+        sampled = eng.generate(prompts, max_tokens=9, stop_ids=[], sampling=SamplingParams(0.9, 40, 0.9, seed=3))
+        results[ahead] = ([(r.tokens, r.reason) for r in greedy], [(r.tokens, r.reason) for r in sampled], eng.stats.decode_steps)
+        assert eng.runner.cache.pages_held() == 0
+    assert results["true"][:2] == results["false"][:2]
+    assert any(reason == "stop" for _, reason in results["true"][0])
+
+
 def test_bfloat16_generation_runs_and_mostly_agrees(model_folders):
     from gemmars_b200 import Engine
     folder = model_folders(TINY_A)

@@ -151,3 +151,52 @@ def test_a_turn_in_a_kept_slot_uses_the_same_decisions_and_leaves_the_slot_open(
         loop.run_in_slot(slot, 39, Request([1, 2], 4))
     m.close(slot)
     assert m.slots.free_count == 2
+
+
+def test_steps_launched_ahead_change_no_decision():
+    """With ``step_ahead`` the next step runs from the drawn tokens before they are read.  The
+    tokens, reasons and what each sequence holds must be what the plain loop gives: a sequence
+    that ends only wastes its row of the step that was already on its way, and the rows of those
+    that go on are picked out of it."""
+    import numpy as np
+
+    class AheadModel(FakeModel):
+        def __init__(self, n):
+            super().__init__(n)
+            self.ahead_calls = 0
+
+        def step(self, items):
+            return np.asarray(super().step(items))
+
+        def step_ahead(self, slots, drawn):
+            self.ahead_calls += 1
+            return self.step([(s, [int(t)]) for s, t in zip(slots, drawn)])
+
+        class Sampler(FakeModel.Sampler):
+            def draw(self, logits, seqs):
+                return list(logits)
+
+            def read(self, drawn):
+                return [int(t) for t in drawn]
+
+    reqs = [Request([1, 2, 3], 6), Request([9], 2), Request([4, 4, 4, 4, 4], 4, stop_ids=(_expected([4] * 5, 4)[0][1],)),
+            Request([7, 1], 1), Request([5, 5], 7)]
+    plain_model = FakeModel(5)
+    want = plain_model.loop(max_batch=5).run(reqs)
+    m = AheadModel(5)
+    loop = GenerationLoop(m.open, m.close, m.step, m.Sampler, 5, 100, 64, None, step_ahead=m.step_ahead)
+    got = loop.run(reqs)
+    assert [(r.tokens, r.reason, r.forwards) for r in got] == [(r.tokens, r.reason, r.forwards) for r in want]
+    assert m.ahead_calls > 0 and loop.ahead_steps > 0 and m.slots.free_count == 5
+    # the last step of a batch is never launched ahead when no sequence can go on after it
+    assert loop.decode_steps == plain_model_steps(reqs, want)
+    # a turn in a kept slot never runs ahead: its last token must stay unrun
+    slot = m.open()
+    before = m.ahead_calls
+    turn = loop.run_in_slot(slot, 0, Request([3, 4], 3))
+    assert m.ahead_calls == before and m.seqs[slot] == [3, 4] + turn.tokens[:-1]
+
+
+def plain_model_steps(reqs, results):
+    """Decode steps a batch needs when none is wasted: as many as its longest-running sequence."""
+    return max(r.forwards for r in results)
