@@ -294,6 +294,10 @@ class SequenceCache:
         start = self.lengths[slot]
         if start + n > self.max_seq_len:
             raise CacheError(f"sequence of {start + n} tokens exceeds the longest the cache holds ({self.max_seq_len})")
+        for g in self.kv_groups:        # all or nothing: no group takes a page unless every group has enough
+            if g.pages_needed(slot, start + n) > g.pages.free_count:
+                raise CacheError(f"the cache is full: {g.pages.free_count} pages are free, slot {slot} needs "
+                                 f"{g.pages_needed(slot, start + n)} more to hold {start + n} tokens")
         for g in self.kv_groups:
             g.reserve(slot, start + n)
         self.lengths[slot] = start + n

@@ -160,3 +160,67 @@ def test_random_walk_keeps_the_books():
     for s in list(live):
         c.close(s)
     assert full.pages.held_count == 0 and win.pages.held_count == 0 and c.slots.free_count == 5
+
+
+def test_random_histories_lose_and_share_nothing():
+    """Any order of opening, extending, truncating, rolling back and closing sequences: at every
+    moment every page a table names is held by exactly one (slot, place), the held pages are the
+    named ones, no page is page 0, lengths fit what is mapped, and at the end everything is back."""
+    from hypothesis import given, settings, strategies as st
+
+    ops = st.lists(st.tuples(st.sampled_from(["open", "extend", "truncate", "rollback", "close"]),
+                             st.integers(0, 7), st.integers(1, 200)), min_size=1, max_size=60)
+
+    @settings(max_examples=150, deadline=None)
+    @given(ops)
+    def run(history):
+        c = _cache([(0, KVNeed(1, 16)), (1, KVNeed(1, 16, window=40)), (2, StateNeed((2,)))], max_tokens=64 * 10, slots=4)
+        full, win = c.kv_groups
+        live = []
+        for op, which, n in history:
+            if op == "open":
+                if c.slots.free_count:
+                    s = c.open()
+                    assert s not in live
+                    live.append(s)
+                else:
+                    with pytest.raises(CacheError):
+                        c.open()
+            elif live:
+                s = live[which % len(live)]
+                if op == "extend":
+                    if c.can_extend([(s, n)]):
+                        assert c.extend(s, n) + n == c.lengths[s]
+                    else:
+                        before = (c.lengths[s], c.pages_held())
+                        with pytest.raises(CacheError):
+                            c.extend(s, n)                       # too long, or not enough pages: nothing is taken
+                        assert (c.lengths[s], c.pages_held()) == before
+                elif op == "truncate":
+                    keep = n % (c.lengths[s] + 1)
+                    if all(g.need.window is None for g in c.kv_groups):
+                        c.truncate(s, keep)
+                elif op == "rollback":
+                    c.rollback(s, n % (c.lengths[s] + 1))
+                elif op == "close":
+                    c.close(s)
+                    live.remove(s)
+            # ---- what must hold at every moment
+            for g in (full, win):
+                named = [int(p) for s in range(c.n_slots) for p in g.table_host[s].tolist() if p]
+                assert len(named) == len(set(named)) == g.pages.held_count and 0 not in named
+                assert g.pages.held_count + g.pages.free_count == g.pages.n
+                assert int(g.table_host[c.n_slots].sum()) == 0                      # the spare row stays empty
+                for s in range(c.n_slots):
+                    if s not in live:
+                        assert int(g.table_host[s].sum()) == 0
+            for s in live:
+                need = -(-c.lengths[s] // 64)
+                assert sum(1 for p in full.table_host[s].tolist() if p) >= need
+                assert sum(1 for p in win.table_host[s].tolist() if p) >= min(need, win.table_width)
+            assert sorted(c.slots.held) == sorted(live) and set(c.lengths) == set(live)
+        for s in live:
+            c.close(s)
+        assert c.pages_held() == 0 and c.slots.free_count == c.n_slots
+
+    run()

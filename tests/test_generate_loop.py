@@ -200,3 +200,44 @@ def test_steps_launched_ahead_change_no_decision():
 def plain_model_steps(reqs, results):
     """Decode steps a batch needs when none is wasted: as many as its longest-running sequence."""
     return max(r.forwards for r in results)
+
+
+def test_random_request_sets_give_each_request_its_own_answer():
+    """Whatever the prompts, limits, stop tokens, batch size and cache size: every request gets the
+    tokens it would get alone, in request order; every slot is given back; with and without steps
+    launched ahead."""
+    import numpy as np
+    from hypothesis import given, settings, strategies as st
+
+    class AheadModel(FakeModel):
+        def step(self, items):
+            return np.asarray(super().step(items))
+
+        def step_ahead(self, slots, drawn):
+            return self.step([(s, [int(t)]) for s, t in zip(slots, drawn)])
+
+        class Sampler(FakeModel.Sampler):
+            def draw(self, logits, seqs):
+                return list(logits)
+
+            def read(self, drawn):
+                return [int(t) for t in drawn]
+
+    request = st.tuples(st.lists(st.integers(0, 49), min_size=1, max_size=12), st.integers(0, 9),
+                        st.lists(st.integers(0, 49), max_size=3))
+
+    @settings(max_examples=120, deadline=None)
+    @given(st.lists(request, min_size=1, max_size=9), st.integers(1, 4), st.booleans())
+    def run(specs, max_batch, ahead):
+        reqs = [Request(p, n, stop_ids=tuple(stop)) for p, n, stop in specs]
+        m = AheadModel(max_batch)
+        loop = GenerationLoop(m.open, m.close, m.step, m.Sampler, max_batch, 50, 64, None,
+                              step_ahead=m.step_ahead if ahead else None)
+        got = loop.run(reqs)
+        assert m.slots.free_count == max_batch and not m.seqs
+        for r, (p, n, stop) in zip(got, specs):
+            want, reason = _expected(p, n, stop)
+            assert (r.tokens, r.reason, r.prompt_tokens) == (want, reason if n > 0 else LENGTH, len(p))
+            assert r.unfed == (want[-1] if want and r.reason != STOP else None)
+
+    run()
