@@ -13,15 +13,12 @@ from __future__ import annotations
 
 import dataclasses
 import os
-import time
 from typing import List, Optional, Sequence
-
-import torch
 
 from .. import kernels
 from ..config.base import load_stop_ids
 from ..sampling.sampler import BatchSampler, SamplingParams
-from .generate import CANCELLED, LENGTH, STOP, Generated, GenerationLoop, Request
+from .generate import Generated, GenerationLoop, Request
 from .model import build_model
 from .step import Runner, StepItem
 

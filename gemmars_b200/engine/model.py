@@ -15,7 +15,6 @@ import torch
 
 from ..config.registry import load_config
 from ..csrc import build
-from ..parts import base as parts_base
 from ..parts.base import StepContext, build_block, build_part, compute_dtype
 from ..parts.plan import ModelPlan
 from ..weights.loader import check_checkpoint, load_checkpoint

@@ -13,7 +13,7 @@ and the walk run in the ``sampling`` CUDA unit.
 from __future__ import annotations
 
 import dataclasses
-from typing import List, Optional, Sequence
+from typing import List, Sequence
 
 import torch
 

@@ -17,7 +17,6 @@ from typing import Dict
 
 import torch
 
-from ..config.base import ModelConfig
 from ..config.registry import resolve_architecture
 from .safetensors_io import write_safetensors
 

@@ -1,7 +1,5 @@
 """Each CUDA kernel alone against a plain PyTorch float32 statement of the same operation, at
 sizes other than the engine's."""
-import math
-
 import pytest
 import torch
 

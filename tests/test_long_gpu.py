@@ -7,7 +7,6 @@ import os
 
 import numpy as np
 import pytest
-import torch
 
 import plain_qwen3 as plain
 from tiny_configs import TINY_B, TOL_BF16
