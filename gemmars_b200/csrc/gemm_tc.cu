@@ -46,6 +46,22 @@ enum { EPI_STORE_BF16 = 0, EPI_STORE_F32 = 1, EPI_ACCUMULATE_F32 = 2, EPI_SWIGLU
 // the value it holds in a register: RMSNorm over the head, rotation at the token's position, the
 // query's scale; queries go to y as bfloat16, keys and values straight into the paged cache
 // (src/qwen.rs:737-785).  What that needs beyond the product:
+// An RMSNorm that sits between two products, taken into them (decode steps, where the norm's own
+// kernel costs more waiting than work).  The product before it, which adds into the residual r,
+// also leaves bf16(r * g), g being the norm's weight, and its tile's part of every token's sum
+// of squares; the product after it takes those rows as its input and multiplies each token's
+// results by 1 / sqrt(mean(r^2) + eps), which is what the norm would have done to its input.
+// Statistics and the scale are float32; the parts are added in tile order (the same bits every run).
+struct NormLink {
+  const float* in_partial;   // this product's input rows are unscaled: [in_tiles][64] sums of squares; null: rows are plain
+  int in_tiles;
+  float in_eps, in_inv_width;
+  const float* out_weight;   // this product adds into the residual and a norm follows: its weight; null: nothing to leave
+  bf16* out_rows;            // [M][N] rows out_ld apart: bf16(residual * weight)
+  long long out_ld;
+  float* out_partial;        // [tiles of this product][64]
+};
+
 struct QkvTail {
   const float* q_weight;    // [128] or null: no norm
   const float* k_weight;
@@ -60,6 +76,7 @@ struct QkvTail {
   int nh, nkv, table_width, page_size;
   const float2* rope_table; // prompts: [tokens][64] (cos, sin) of each packed token's angles, or null
   const int2* token_place;  // prompts: [tokens] (page, position in the page) of each packed token
+  NormLink link;            // any mode of gemm_tc_kernel: a norm taken into this product (all null: none)
 };
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
 
@@ -505,10 +522,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int real = min(M - m0, BN), share = (real + (int)nsplit - 1) / (int)nsplit;
   const int c0 = min(real, (int)split * share), c1 = min(real, c0 + share);
   float bias_v = 0.f, old[8];
+  __shared__ float row_scale[64], sq_part[4][32];
+  const NormLink& link = tail.link;
   if (warp < 4) {
     pdl_wait_prior();   // y may be read (accumulate) and is written: not before the kernel before is done
     const int n = n0 + warp * 32 + lane;
     bias_v = (bias && n < N) ? bias[n] : 0.f;
+    if (link.in_partial) {
+      // The scale of each of the tile's tokens, while the products run.  A token's sums of squares
+      // (one per tile of the product that left them) are shared out over 128 / BN adjacent lanes,
+      // four loads in flight each, and added up in a fixed order: the same bits every run.
+      constexpr int TOK = BN < 64 ? BN : 64, PER = 128 / TOK;      // PER: 8, 4 or 2 lanes a token
+      const int t = warp * 32 + lane, tok = t / PER, j = t % PER;
+      float ss = 0.f;
+      if (m0 + tok < M) {
+        const float* col = link.in_partial + m0 + tok;
+        for (int i = j; i < link.in_tiles; i += 4 * PER) {
+          const float a = col[i * 64];
+          const float b = i + PER < link.in_tiles ? col[(i + PER) * 64] : 0.f;
+          const float c = i + 2 * PER < link.in_tiles ? col[(i + 2 * PER) * 64] : 0.f;
+          const float d = i + 3 * PER < link.in_tiles ? col[(i + 3 * PER) * 64] : 0.f;
+          ss += (a + b) + (c + d);
+        }
+      }
+#pragma unroll
+      for (int o = 1; o < PER; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (j == 0) row_scale[tok] = 1.0f / sqrtf(ss * link.in_inv_width + link.in_eps);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     if (MODE == EPI_ACCUMULATE_F32 && nsplit > 1) {
       // what this thread will add to: asked for now, so that the answer is there after the products
 #pragma unroll
@@ -564,6 +605,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     cluster_sync();
     if (warp < 4) {
       const int f = warp * 32 + lane, n = n0 + f;
+      const float out_g = (MODE == EPI_ACCUMULATE_F32 && link.out_weight && n < N) ? link.out_weight[n] : 0.f;
 #pragma unroll 1
       for (int c = c0; c < c1; ++c) {
         const float* mine = recv + ((size_t)(c - c0) * NACC) * BM + f;
@@ -577,26 +619,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         float sum = part[0];
 #pragma unroll
         for (int r = 1; r < 8; ++r) sum += part[r];
+        const float sc = link.in_partial ? row_scale[c] : 1.f;
+        sum *= sc;
         if (MODE == EPI_QKV_BF16) {   // every thread has the same tokens: they finish one together
           qkv_finish(tail, y, ldy, m0 + c, n0, f, sum + bias_v, qkv_red, qkv_xs);
           continue;
         }
-        if (n >= N) continue;
-        if (DUAL) {
-          float up = part_up[0];
+        float final_r = 0.f;
+        if (n < N) {
+          if (DUAL) {
+            float up = part_up[0];
 #pragma unroll
-          for (int r = 1; r < 8; ++r) up += part_up[r];
-          sum = silu_mul(sum, up);
-        }
-        const size_t idx = (size_t)(m0 + c) * ldy + n;
-        if (MODE == EPI_ACCUMULATE_F32) {
-          float prev = c - c0 < 8 ? 0.f : ((const float*)y)[idx];   // the first eight were asked for early
+            for (int r = 1; r < 8; ++r) up += part_up[r];
+            sum = silu_mul(sum, up * sc);
+          }
+          const size_t idx = (size_t)(m0 + c) * ldy + n;
+          if (MODE == EPI_ACCUMULATE_F32) {
+            float prev = c - c0 < 8 ? 0.f : ((const float*)y)[idx];   // the first eight were asked for early
 #pragma unroll
-          for (int q = 0; q < 8; ++q) prev = (c - c0 == q) ? old[q] : prev;
-          ((float*)y)[idx] = prev + sum + bias_v;
-        } else {
-          emit<MODE>(y, idx, sum + bias_v);
+            for (int q = 0; q < 8; ++q) prev = (c - c0 == q) ? old[q] : prev;
+            final_r = prev + sum + bias_v;
+            ((float*)y)[idx] = final_r;
+            if (link.out_weight) link.out_rows[(size_t)(m0 + c) * link.out_ld + n] = __float2bfloat16_rn(final_r * out_g);
+          } else {
+            emit<MODE>(y, idx, sum + bias_v);
+          }
         }
+        if (MODE == EPI_ACCUMULATE_F32 && link.out_weight) {   // this warp's 32 features of the token's sum of squares
+          const float sq = warp_sum(final_r * final_r);
+          if (lane == 0 && c - c0 < 32) sq_part[warp][c - c0] = sq;
+        }
+      }
+      if (MODE == EPI_ACCUMULATE_F32 && link.out_weight) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int t = warp * 32 + lane;
+        if (t < c1 - c0)
+          link.out_partial[(size_t)blockIdx.y * 64 + m0 + c0 + t] = sq_part[0][t] + sq_part[1][t] + sq_part[2][t] + sq_part[3][t];
       }
     }
   } else if (warp < 4 && have_acc) {
@@ -614,6 +672,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       acc_load<DUAL>(acc, BN, c, v, u);
       if (BOTH) acc_load<DUAL>(acc, BN, c + 16, v2, u2);
       tc_wait_ld();
+      if (link.in_partial) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float s1 = row_scale[c + j], s2 = BOTH ? row_scale[c + 16 + j] : 1.f;
+          v[j] = __float_as_uint(__uint_as_float(v[j]) * s1);
+          if (DUAL) u[j] = __float_as_uint(__uint_as_float(u[j]) * s1);
+          if (BOTH) v2[j] = __float_as_uint(__uint_as_float(v2[j]) * s2);
+          if (BOTH && DUAL) u2[j] = __float_as_uint(__uint_as_float(u2[j]) * s2);
+        }
+      }
       gate<DUAL>(v, u);
       if (BOTH) gate<DUAL>(v2, u2);
       if (by_tma) {
@@ -946,11 +1014,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const
 
 template <int BN, int STAGES>
 int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
-                int N, int K, long long ldy, int splits, cudaStream_t stream) {
+                int N, int K, long long ldy, int splits, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
   switch (mode) {
-    case EPI_STORE_BF16: return launch<BN, STAGES, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-    case EPI_STORE_F32: return launch<BN, STAGES, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-    case EPI_ACCUMULATE_F32: return launch<BN, STAGES, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+    case EPI_STORE_BF16: return launch<BN, STAGES, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+    case EPI_STORE_F32: return launch<BN, STAGES, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+    case EPI_ACCUMULATE_F32: return launch<BN, STAGES, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
   }
   return GB_ERR_ARG;
 }
@@ -984,9 +1052,15 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
 // splits: CTAs of a cluster sharing the inner dimension (1, 2, 4, 8; only with bn <= 64);
 // stages: pipeline depth for bn <= 64 (4 or 8; other tiles have a fixed depth).
 // Needs K % 8 == 0, ldx % 8 == 0 and 16-byte aligned x and w (TMA rules).
-GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N, int K,
-                         long long ldx, long long ldy, int bn, int splits, int stages, cudaStream_t stream) {
+static int gemm_tc_with_link(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N, int K,
+                             long long ldx, long long ldy, int bn, int splits, int stages, const NormLink& link,
+                             cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  QkvTail tail{};
+  tail.link = link;
+  if (link.in_partial && (M > 64 || bn > 64 || link.in_tiles <= 0)) return GB_ERR_SIZE;
+  // leaving rows for a norm is the work of the ranks that finish a token: it needs the inner dimension split
+  if (link.out_weight && (mode != EPI_ACCUMULATE_F32 || splits < 2 || M > 64 || !link.out_rows || !link.out_partial)) return GB_ERR_ARG;
   if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return GB_ERR_SIZE;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return GB_ERR_ARG;
   if (splits > 1 && bn > 64) return GB_ERR_ARG;
@@ -998,11 +1072,11 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
   const OutMap my = out_map(y, mode, M, N, ldy, bn);
   if (swiglu) {
     switch (bn) {
-      case 16: return launch<16, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-      case 32: return launch<32, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-      case 64: return launch<64, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-      case 128: return launch<128, 4, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-      case 256: return launch<256, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      case 16: return launch<16, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+      case 32: return launch<32, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+      case 64: return launch<64, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+      case 128: return launch<128, 4, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+      case 256: return launch<256, 3, EPI_SWIGLU_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
     }
     return GB_ERR_SIZE;
   }
@@ -1010,20 +1084,39 @@ GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* 
     // decoding: `stages` = 4 leaves room for three CTAs on an SM (their tiles then finish together),
     // 8 gives one CTA a deeper pipeline
     case 16:
-      return stages == 8 ? launch_mode<16, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<16, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 8 ? launch_mode<16, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail)
+                         : launch_mode<16, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
     case 32:
-      return stages == 8 ? launch_mode<32, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<32, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 8 ? launch_mode<32, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail)
+                         : launch_mode<32, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
     case 64:
-      return stages == 8 ? launch_mode<64, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<64, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 8 ? launch_mode<64, 8>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail)
+                         : launch_mode<64, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
     case 128:   // stages = 3: two CTAs fit an SM, and one's epilogue runs under the other's MMAs
-      return stages == 3 ? launch_mode<128, 3>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream)
-                         : launch_mode<128, 6>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
-    case 256: return launch_mode<256, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream);
+      return stages == 3 ? launch_mode<128, 3>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail)
+                         : launch_mode<128, 6>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
+    case 256: return launch_mode<256, 4>(mode, mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
   }
   return GB_ERR_SIZE;
+}
+
+GB_EXPORT int gb_gemm_tc(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N, int K,
+                         long long ldx, long long ldy, int bn, int splits, int stages, cudaStream_t stream) {
+  return gemm_tc_with_link(x, w, bias, y, mode, M, N, K, ldx, ldy, bn, splits, stages, NormLink{}, stream);
+}
+
+// gb_gemm_tc with an RMSNorm taken into it (see NormLink; at most 64 tokens).  in_partial non-null:
+// x holds bf16(residual * norm weight) and every token's results are multiplied by
+// 1 / sqrt(sum of in_partial[0 .. in_tiles)[token] / in_width + in_eps).  out_weight non-null
+// (mode 2, splits >= 2): besides adding into y, the kernel writes bf16(y * out_weight) to out_rows
+// (rows out_ld apart) and this product's tiles' sums of squares to out_partial [ceil(N / 128)][64].
+GB_EXPORT int gb_gemm_tc_linked(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N, int K,
+                                long long ldx, long long ldy, int bn, int splits, int stages, const float* in_partial,
+                                int in_tiles, float in_eps, int in_width, const float* out_weight, void* out_rows,
+                                long long out_ld, float* out_partial, cudaStream_t stream) {
+  NormLink link{in_partial, in_tiles, in_eps, in_width > 0 ? 1.0f / (float)in_width : 0.f, out_weight, (bf16*)out_rows, out_ld,
+                out_partial};
+  return gemm_tc_with_link(x, w, bias, y, mode, M, N, K, ldx, ldy, bn, splits, stages, link, stream);
 }
 
 // The q/k/v product of a decode step with the per-head work in its epilogue (head size 128, at most
@@ -1034,10 +1127,12 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, const float* bias, vo
                              long long ldy, int bn, int splits, const float* q_weight, const float* k_weight,
                              const float* inv_freq, float eps, float q_scale, int nh, int nkv, const int* tok_pos,
                              const int* tok_seq, const int* seq_slot, const int* page_table, int table_width,
-                             int page_size, void* kcache, void* vcache, cudaStream_t stream) {
+                             int page_size, void* kcache, void* vcache, const float* in_partial, int in_tiles,
+                             float in_eps, int in_width, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return GB_ERR_SIZE;
   if (splits != 1 && splits != 2 && splits != 4 && splits != 8) return GB_ERR_ARG;
+  if (in_partial && (in_tiles <= 0 || in_width <= 0)) return GB_ERR_ARG;
   if (M > 64 || nh <= 0 || nkv < 0 || N != (nh + 2 * nkv) * BM || !tok_pos) return GB_ERR_SIZE;
   if (page_table && (!tok_seq || !seq_slot || !kcache || !vcache || page_size <= 0)) return GB_ERR_ARG;
   if ((q_weight == nullptr) != (k_weight == nullptr)) return GB_ERR_ARG;
@@ -1047,6 +1142,10 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, const float* bias, vo
   const OutMap my = out_map(y, EPI_QKV_BF16, M, N, ldy, bn);   // not used: the tail writes to the cache
   QkvTail tail{q_weight, k_weight, inv_freq, tok_pos, tok_seq, seq_slot, page_table, (bf16*)kcache, (bf16*)vcache,
                eps, q_scale, nh, nkv, table_width, page_size};
+  tail.link.in_partial = in_partial;     // x holds unscaled rows: see NormLink
+  tail.link.in_tiles = in_tiles;
+  tail.link.in_eps = in_eps;
+  tail.link.in_inv_width = in_partial ? 1.0f / (float)in_width : 0.f;
   switch (bn) {
     case 16: return launch<16, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);
     case 32: return launch<32, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, splits, stream, tail);

@@ -133,11 +133,20 @@ class DecoderModel:
         ctx.extras.clear()
         x = torch.empty((tokens.numel(), self.plan.hidden_size), dtype=torch.float32, device=self.device)
         self.embedding.forward(ctx, tokens, x)
-        for i, e in enumerate(self.plan.schedule):
+        carry = None          # what a block's last product left for the next block's first norm
+        schedule = self.plan.schedule
+        for i, e in enumerate(schedule):
             owner = i if e.cache_of is None else e.cache_of
             block = self.blocks[e.layer]
             ctx.extras["entry"] = i
-            block.forward(ctx, x, ctx.cache.views(owner), writes_cache=e.cache_of is None)
+            if getattr(block, "chains_norms", False):
+                after = self.blocks[schedule[i + 1].layer] if i + 1 < len(schedule) else None
+                next_norm = after.first_norm() if getattr(after, "chains_norms", False) else None
+                carry = block.forward(ctx, x, ctx.cache.views(owner), writes_cache=e.cache_of is None, h_in=carry,
+                                      next_norm=next_norm)
+            else:
+                block.forward(ctx, x, ctx.cache.views(owner), writes_cache=e.cache_of is None)
+                carry = None
         return x
 
     def logits(self, ctx: StepContext, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:

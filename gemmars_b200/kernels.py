@@ -319,10 +319,48 @@ def gemm_tc_tiling(m: int, n: int, k: int, gated: bool = False, sms: Optional[in
     return best, 1
 
 
-def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages=4, swiglu=False):
+class UnscaledRows:
+    """The input of an RMSNorm that is taken into the products around it (decode steps): ``rows``
+    [tokens, width] = bfloat16(residual * the norm's weight), and ``partial`` [tiles, 64], the
+    sums of squares of the residual's rows in tiles of 128 features, both left by the product
+    that added into the residual.  The norm's output is rows * rstd, rstd[t] = (sum of
+    partial[:, t] / width + eps) ** -0.5; the product that takes these rows applies rstd to its
+    results instead (float32), so the norm needs no kernel of its own."""
+
+    def __init__(self, rows, partial, eps: float, width: int):
+        self.rows, self.partial, self.eps, self.width = rows, partial, float(eps), int(width)
+
+    @property
+    def shape(self):
+        return self.rows.shape
+
+    def materialize(self) -> torch.Tensor:
+        """The norm's output as a plain tensor, for a consumer that cannot take unscaled rows."""
+        m = self.rows.shape[0]
+        rstd = (self.partial[:, :m].sum(0) / self.width + self.eps).rsqrt()
+        return (self.rows.float() * rstd[:, None]).to(self.rows.dtype)
+
+
+LINK_MAX_TOKENS = 64
+
+
+def norm_link_usable(x, w, m: int, accumulate_splits: Optional[int] = None) -> bool:
+    """Whether gemm_tc can take an RMSNorm into itself for these operands: at most 64 tokens on
+    the tensor-core path; the product that leaves the rows must have its inner dimension split."""
+    ok = m <= LINK_MAX_TOKENS and gemm_tc_usable(x, w)
+    return ok and (accumulate_splits is None or accumulate_splits >= 2)
+
+
+def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages=4, swiglu=False, link_in=None,
+            link_out=None):
     """out = x @ w.T (+ bias) (bfloat16 or float32 out) or out += ... (float32 out), bfloat16
     operands, on the tcgen05 tensor cores.  With ``swiglu``, w stacks a gate matrix over an up
-    matrix ([2N, K]) and out[M, N] = silu(x @ gate.T) * (x @ up.T) in bfloat16."""
+    matrix ([2N, K]) and out[M, N] = silu(x @ gate.T) * (x @ up.T) in bfloat16.
+    ``link_in``: an UnscaledRows whose ``rows`` are x: every token's results are scaled by its
+    rstd.  ``link_out`` = (norm weight float32 [N], eps): with ``accumulate``, also leaves
+    bfloat16(out * weight) and the sums of squares of out's rows, returned as UnscaledRows."""
+    if link_in is not None:
+        assert x is link_in.rows
     _cuda(x, w, out, bias)
     m, k = x.shape
     n = w.shape[0] // 2 if swiglu else w.shape[0]
@@ -341,12 +379,38 @@ def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages
     if bias is not None:
         assert bias.dtype == torch.float32 and bias.numel() == n
     auto_bn, auto_splits = gemm_tc_tiling(m, n, k, gated=swiglu)
-    f = _fn("gemm_tc", "gb_gemm_tc",
+    if link_in is None and link_out is None:
+        f = _fn("gemm_tc", "gb_gemm_tc",
+                [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
+                 c_int, c_int, c_void_p])
+        _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
+                 bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc", "matmul",
+               _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
+        return None
+    if m > LINK_MAX_TOKENS:
+        raise KernelError(f"gemm_tc: a norm can be taken into the product for at most {LINK_MAX_TOKENS} tokens")
+    left = None
+    if link_out is not None:
+        weight, eps = link_out
+        if not accumulate or (splits or auto_splits) < 2:
+            raise KernelError("gemm_tc: rows for a norm are left by a product that adds into the residual with its "
+                              "inner dimension split")
+        assert weight.dtype == torch.float32 and weight.numel() == n
+        left = UnscaledRows(torch.empty((m, n), dtype=torch.bfloat16, device=x.device),
+                            torch.empty((-(-n // 128), 64), dtype=torch.float32, device=x.device), eps, n)
+    f = _fn("gemm_tc", "gb_gemm_tc_linked",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
-             c_int, c_int, c_void_p])
+             c_int, c_int, c_void_p, c_int, c_float, c_int, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0),
-             bn or auto_bn, splits or auto_splits, stages, _stream()), "gemm_tc", "matmul",
-           _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
+             bn or auto_bn, splits or auto_splits, stages,
+             link_in.partial.data_ptr() if link_in is not None else None,
+             link_in.partial.shape[0] if link_in is not None else 0, link_in.eps if link_in is not None else 0.0,
+             link_in.width if link_in is not None else 0,
+             link_out[0].data_ptr() if left is not None else None, left.rows.data_ptr() if left is not None else None,
+             left.rows.stride(0) if left is not None else 0, left.partial.data_ptr() if left is not None else None,
+             _stream()), "gemm_tc", "matmul",
+           _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0) + (_nbytes(left.rows) if left is not None else 0))
+    return left
 
 
 def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=None):
@@ -403,7 +467,7 @@ def gemm_qkv_usable(x, w, nh: int, nkv: int, hd: int, rot: int, limit: Optional[
 
 
 def gemm_qkv(x, w, bias, qkv, nh, nkv, hd, q_weight, k_weight, eps, inv_freq, q_scale, tok_pos, tok_seq, seq_slot,
-             page_table, page_size, kcache, vcache, bn=None, splits=None):
+             page_table, page_size, kcache, vcache, bn=None, splits=None, link_in=None):
     """qkv[:, :nh*hd] = the step's queries, normed per head, rotated and scaled; the keys (normed,
     rotated) and the values go into the paged cache (``page_table`` None: into qkv as well): the
     q/k/v product and head_norm_rope_cache in one kernel.  See gemm_qkv_usable."""
@@ -422,11 +486,16 @@ def gemm_qkv(x, w, bias, qkv, nh, nkv, hd, q_weight, k_weight, eps, inv_freq, q_
     f = _fn("gemm_tc", "gb_gemm_tc_qkv",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_int,
              c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_int, c_int, c_void_p, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_void_p])
+    if link_in is not None:
+        assert x is link_in.rows
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), qkv.data_ptr(), m, n, k, x.stride(0), qkv.stride(0),
              bn or auto_bn, splits or auto_splits, _ptr(q_weight), _ptr(k_weight), _ptr(inv_freq), eps, q_scale, nh, nkv,
              tok_pos.data_ptr(), _ptr(tok_seq), _ptr(seq_slot), _ptr(page_table),
-             page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache), _ptr(vcache), _stream()),
+             page_table.shape[1] if page_table is not None else 1, page_size, _ptr(kcache), _ptr(vcache),
+             link_in.partial.data_ptr() if link_in is not None else None,
+             link_in.partial.shape[0] if link_in is not None else 0, link_in.eps if link_in is not None else 0.0,
+             link_in.width if link_in is not None else 0, _stream()),
            "gemm_qkv", "matmul", _nbytes(x, w, bias, qkv))
 
 
@@ -494,7 +563,14 @@ def gemm_qkv_prompt(x, w, bias, q_out, nh, nkv, hd, q_weight, k_weight, eps, tab
 
 def gemm_swiglu(x, w_gate_up, out):
     """out[M, N] = silu(x @ gate.T) * (x @ up.T) for w_gate_up = [gate; up] of 2N rows: one
-    tensor-core kernel in bfloat16; two kernels (product, then activation) otherwise."""
+    tensor-core kernel in bfloat16; two kernels (product, then activation) otherwise.  ``x`` may
+    be UnscaledRows (a norm taken into this product)."""
+    link = x if isinstance(x, UnscaledRows) else None
+    if link is not None:
+        if norm_link_usable(link.rows, w_gate_up, link.rows.shape[0]):
+            gemm_tc(link.rows, w_gate_up, out, swiglu=True, link_in=link)
+            return
+        x = link.materialize()
     if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w_gate_up):
         if x.shape[0] > 64:
             gemm_tc_persistent(x, w_gate_up, out, swiglu=True)
@@ -749,19 +825,36 @@ def gemm_units(compute: str):
     return [("gemm_ref", ())] if compute == "float32" else [("gemm_tc", ()), ("gemm_ref", ())]
 
 
-def gemm(x, w, out, bias=None, accumulate=False):
+# Whether the blocks take the RMSNorms of a decode step into the products around them (see
+# UnscaledRows).  Measured as an upper bound, by skipping the norm kernels: 2 % of a step at 8B layer
+# sizes, 5.6 % at 4B sizes.
+NORM_LINKS = True
+
+
+def gemm(x, w, out, bias=None, accumulate=False, then_norm=None):
     """out = x @ w.T (+ bias) or, with ``accumulate``, out += ...; picks the kernel for the
     precision and the shape: float32 runs on the CUDA cores in a fixed order; bfloat16 runs on the
     tensor cores, except for operands whose rows TMA cannot address (an inner size that is not
-    a multiple of 8), which the plain kernel takes."""
-    if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w):
-        m, n = x.shape[0], w.shape[0]
-        if x.shape[0] > 64:
-            gemm_tc_persistent(x, w, out, bias, accumulate)
+    a multiple of 8), which the plain kernel takes.  ``x`` may be UnscaledRows (a norm taken into
+    this product).  ``then_norm`` = (weight, eps) of an RMSNorm that follows an accumulating
+    product: where the kernel can, it leaves that norm's input as UnscaledRows, which is returned
+    (None: the norm has to run by itself)."""
+    link = x if isinstance(x, UnscaledRows) else None
+    if link is not None:
+        if norm_link_usable(link.rows, w, link.rows.shape[0]):
+            x = link.rows
         else:
-            gemm_tc(x, w, out, bias, accumulate)
-    else:
-        gemm_ref(x, w, out, bias, accumulate)
+            x, link = link.materialize(), None
+    if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w):
+        m, n, k = x.shape[0], w.shape[0], x.shape[1]
+        if m > 64:
+            gemm_tc_persistent(x, w, out, bias, accumulate)
+            return None
+        if then_norm is not None and not (accumulate and gemm_tc_tiling(m, n, k)[1] >= 2):
+            then_norm = None
+        return gemm_tc(x, w, out, bias, accumulate, link_in=link, link_out=then_norm)
+    gemm_ref(x, w, out, bias, accumulate)
+    return None
 
 
 def attention_units(compute: str, head_dim: int):

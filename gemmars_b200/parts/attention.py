@@ -104,8 +104,17 @@ class Attention(Part):
                                                       group.page_size)
         return t
 
+    #: forward takes ``then_norm`` and may be given kernels.UnscaledRows for ``h``
+    links_norms = True
+
     # ---- step
-    def forward(self, ctx, h, residual, caches, writes_cache=True):
+    def forward(self, ctx, h, residual, caches, writes_cache=True, then_norm=None):
+        """``h``: the normed activations, or kernels.UnscaledRows (the norm before is taken into
+        the q/k/v product).  ``then_norm``: the RMSNorm that reads the residual next; returns that
+        norm's input where the o product could leave it, else None."""
+        link = h if isinstance(h, kernels.UnscaledRows) else None
+        if link is not None:
+            h = link.rows
         nh, hd = self.num_heads, self.head_dim
         nkv = self.num_kv_heads if self.has_kv else 0
         group, kc, vc = caches[0]
@@ -120,11 +129,12 @@ class Attention(Part):
                              self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps,
                              self.position.inv_freq(h.device) if rot else None, self.scale, ctx.tok_pos, ctx.tok_seq,
                              ctx.seq_slot, group.page_table if writes_cache else None, group.page_size,
-                             kc if writes_cache else None, vc if writes_cache else None)
+                             kc if writes_cache else None, vc if writes_cache else None, link_in=link)
             att = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
             kernels.attention(ctx, qkv[:, :nh * hd], att, nh, kc, vc, group.page_table, group.page_size, self.window)
-            self.o.add_into(att, residual)
-            return
+            return self.o.add_into(att, residual, then_norm)
+        if link is not None and h.shape[0] > kernels.LINK_MAX_TOKENS:
+            h, link = link.materialize(), None
         if (rotary and writes_cache == self.has_kv
                 and kernels.gemm_qkv_prompt_usable(h, self.qkv.weight, nh, nkv, hd, rot, group.page_size)):
             # a prompt step with heads of 128: the same on the prompt product's epilogue; the queries
@@ -137,9 +147,8 @@ class Attention(Part):
                                     kc if nkv else None, vc if nkv else None)
             att = torch.empty_like(q)
             kernels.attention(ctx, q, att, nh, kc, vc, group.page_table, group.page_size, self.window)
-            self.o.add_into(att, residual)
-            return
-        qkv = self.qkv(h)
+            return self.o.add_into(att, residual, then_norm)
+        qkv = self.qkv(link if link is not None else h)
         norm = kernels.FLAG_NORM if self.qk_norm else 0
         store = kernels.FLAG_CACHE if writes_cache else 0
         if ctx.max_new <= 1:
@@ -165,7 +174,7 @@ class Attention(Part):
                                          store | kernels.FLAG_INPLACE)
         att = torch.empty((qkv.shape[0], nh * hd), dtype=qkv.dtype, device=qkv.device)
         kernels.attention(ctx, qkv[:, :nh * hd], att, nh, kc, vc, group.page_table, group.page_size, self.window)
-        self.o.add_into(att, residual)
+        return self.o.add_into(att, residual, then_norm)
 
 
 register_part("mixer", "attention", Attention)

@@ -33,10 +33,16 @@ class GatedMLP(Part):
     def kernel_units(self):
         return kernels.gemm_units(self.compute) + [("elementwise", ())]
 
-    def forward(self, ctx, h, residual):
-        a = torch.empty((h.shape[0], self.intermediate_size), dtype=h.dtype, device=h.device)
+    #: forward takes ``then_norm`` and may be given kernels.UnscaledRows for ``h``
+    links_norms = True
+
+    def forward(self, ctx, h, residual, then_norm=None):
+        """``h``: the normed activations, or kernels.UnscaledRows.  ``then_norm``: the RMSNorm that
+        reads the residual next; returns that norm's input where the down product could leave it."""
+        rows = h.rows if isinstance(h, kernels.UnscaledRows) else h
+        a = torch.empty((rows.shape[0], self.intermediate_size), dtype=rows.dtype, device=rows.device)
         kernels.gemm_swiglu(h, self.gate_up.weight, a)
-        self.down.add_into(a, residual)
+        return self.down.add_into(a, residual, then_norm)
 
     def weight_bytes(self):
         return self.gate_up.bytes() + self.down.bytes()

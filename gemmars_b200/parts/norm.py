@@ -11,6 +11,9 @@ from .base import Part, TensorWant, register_part
 
 class RMSNorm(Part):
     category = "norm"
+    #: the products around this norm may take it into themselves (kernels.UnscaledRows): its
+    #: output is x * rstd(x) * weight with the weight as stored
+    linkable = True
 
     def __init__(self, spec, compute):
         super().__init__(spec, compute)

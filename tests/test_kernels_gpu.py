@@ -576,3 +576,60 @@ def test_gemm_qkv_prompt_against_product_then_head_kernel(k, nh, nkv, kk, bias, 
     assert float(k1[0].abs().sum()) == 0.0 and float(v1[0].abs().sum()) == 0.0          # nothing strays into page 0
     assert torch.equal(k0 != 0, k1 != 0) or (k0 - k1).abs().max().item() <= 2 ** -6      # the same places are written
     assert k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("m,h,inter,bias", [(1, 256, 384, False), (8, 512, 640, True), (16, 384, 512, False), (33, 256, 896, True),
+                                            (64, 512, 256, False)])
+def test_a_norm_taken_into_the_products_around_it(k, m, h, inter, bias):
+    """The product that adds into the residual also leaves bfloat16(residual * norm weight) and the
+    rows' sums of squares; the products after it (plain, gated, and q/k/v with the per-head work)
+    scale their results by each row's rstd.  Against the residual, an RMSNorm and the products
+    stated in PyTorch float32."""
+    torch.manual_seed(m + h)
+    eps = 1e-5
+    a = (torch.randn(m, inter, device="cuda") * 0.5).bfloat16()
+    w_down = (torch.randn(h, inter, device="cuda") * 0.05).bfloat16()
+    b_down = (torch.randn(h, device="cuda") * 0.1) if bias else None
+    g = torch.rand(h, device="cuda") + 0.5
+    residual = torch.randn(m, h, device="cuda") * 2
+    want_res = residual + a.float() @ w_down.float().T + (b_down if bias else 0)
+    res = residual.clone()
+    left = k.gemm_tc(a, w_down, res, b_down, accumulate=True, splits=4, link_out=(g, eps))
+    assert (res - want_res).abs().max().item() <= 1e-4 * want_res.abs().max().item()
+    normed = want_res * (want_res.pow(2).mean(-1, keepdim=True) + eps).rsqrt() * g
+    got_normed = left.materialize().float()
+    assert (got_normed - normed).abs().max().item() <= 2 ** -7 * normed.abs().max().item()
+    assert left.partial.shape == (-(-h // 128), 64)
+    # a plain product after the norm
+    w2 = (torch.randn(200, h, device="cuda") * 0.05).bfloat16()
+    b2 = torch.randn(200, device="cuda") * 0.1
+    out = torch.zeros(m, 200, device="cuda", dtype=torch.bfloat16)
+    k.gemm_tc(left.rows, w2, out, b2, link_in=left)
+    ref = normed @ w2.float().T + b2
+    assert (out.float() - ref).abs().max().item() <= 2 ** -6 * ref.abs().max().item()
+    # with the inner dimension split as well
+    out.zero_()
+    k.gemm_tc(left.rows, w2, out, b2, link_in=left, splits=2)
+    assert (out.float() - ref).abs().max().item() <= 2 ** -6 * ref.abs().max().item()
+    # the gated product after the norm
+    wgu = (torch.randn(2 * 320, h, device="cuda") * 0.05).bfloat16()
+    act = torch.zeros(m, 320, device="cuda", dtype=torch.bfloat16)
+    for splits in (1, 2):
+        act.zero_()
+        k.gemm_tc(left.rows, wgu, act, swiglu=True, link_in=left, splits=splits)
+        gate, up = normed @ wgu[:320].float().T, normed @ wgu[320:].float().T
+        ref_act = torch.nn.functional.silu(gate) * up
+        assert (act.float() - ref_act).abs().max().item() <= 2 ** -6 * max(1.0, ref_act.abs().max().item()), splits
+    # the q/k/v product with the per-head work in its epilogue (queries only: no cache here)
+    nh, hd = 2, 128
+    wq = (torch.randn(nh * hd, h, device="cuda") * 0.05).bfloat16()
+    qw = torch.rand(hd, device="cuda") + 0.5
+    tok_pos = torch.arange(m, dtype=torch.int32, device="cuda")
+    tok_seq = torch.zeros(m, dtype=torch.int32, device="cuda")
+    q = torch.zeros(m, nh * hd, device="cuda", dtype=torch.bfloat16)
+    k.gemm_qkv(left.rows, wq, None, q, nh, 0, hd, qw, qw, 1e-6, None, 0.5, tok_pos, tok_seq, tok_seq, None, 64, None, None,
+               link_in=left)
+    z = (normed @ wq.float().T).view(m, nh, hd)
+    ref_q = (z * (z.pow(2).mean(-1, keepdim=True) + 1e-6).rsqrt() * qw * 0.5).view(m, nh * hd)
+    assert (q.float() - ref_q).abs().max().item() <= 2 ** -6 * ref_q.abs().max().item()
+    assert k.gemm_tc_status() == 0
