@@ -28,6 +28,14 @@ Interfaces (all tensors on the device; ``ctx`` is the ``StepContext`` of the run
   needs in the order of ``parts()`` (``Block.split_caches`` deals them out).
 * embedding: ``forward(ctx, tokens, out)``; head: ``forward(ctx, h)`` -> float32 logits.
 
+Optional, for decode steps: a norm taken into the products around it.  A mixer or feed-forward
+whose class says ``links_norms = True`` takes one more argument, ``then_norm`` (the norm part that
+reads the residual after it, or None), may be given ``kernels.UnscaledRows`` instead of a tensor
+for ``h``, and returns what its last product left for ``then_norm`` (``UnscaledRows``) or None.  A
+norm that says ``linkable = True`` can be taken in this way; a block that says ``chains_norms =
+True`` takes ``h_in`` and ``next_norm`` and has ``first_norm()``.  Parts and blocks that say
+nothing are given plain tensors and called as listed above.
+
 Rows that belong to no sequence.  A decode step that is replayed from a captured graph is padded
 to a fixed number of rows.  The padding rows are sequences of one token whose slot is
 ``ctx.pad_slot``: the spare last row of every page table (all page 0) and of every state tensor.
