@@ -262,6 +262,10 @@ def test_attention_decode_stream_against_plain(k, hd, nh, nkv, window, ring):
         k.attention_decode_stream(q, out, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, ctas=ctas)
         err = (out.float() - ref).abs().max().item()
         assert err <= 2 ** -7 * max(1.0, ref.abs().max().item()), f"ctas={ctas}: {err}"
+        # with the pages of earlier positions asked for ahead of the kernel before: the same bits
+        ahead = torch.zeros_like(q)
+        k.attention_decode_stream(q, ahead, nh, kc, vc, table, 64, tok_pos, tok_seq, seq_slot, window, ctas=ctas, newest=1)
+        assert torch.equal(ahead, out)
     # rows that belong to no sequence (the slot that pads a captured step), first, in the middle and
     # last: nothing is read for them, their rows are zero, the others as before
     skip = 1000
