@@ -149,12 +149,65 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
   }
 }
 
+// The same for rows of up to 32 * 4 * U values: the row stays in the lane's registers (U 16-byte
+// loads in flight at once, nothing read twice).  A prompt of 2,048 rows of 4,096: 20 us with the
+// kernel above inside a prompt step, where the rows come out of L2.
+template <int U>
+__global__ void __launch_bounds__(128) rmsnorm_rows_held_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                bf16* __restrict__ out, const int* __restrict__ rows_index,
+                                                                int rows, int n, float eps) {
+  pdl_release_next();
+  pdl_wait_prior();
+  const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const float4* row4 = (const float4*)(x + (size_t)(rows_index ? rows_index[r] : r) * n);
+  const float4* w4 = (const float4*)w;
+  const int n4 = n / 4;
+  float4 v[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int i = lane + 32 * u;
+    v[u] = i < n4 ? row4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < U; ++u) ss += v[u].x * v[u].x + v[u].y * v[u].y + v[u].z * v[u].z + v[u].w * v[u].w;
+  const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + eps);
+  uint2* o = (uint2*)(out + (size_t)r * n);
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int i = lane + 32 * u;
+    if (i < n4) {
+      const float4 g = w4[i];
+      __nv_bfloat162 lo = __floats2bfloat162_rn(v[u].x * inv * g.x, v[u].y * inv * g.y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(v[u].z * inv * g.z, v[u].w * inv * g.w);
+      o[i] = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+    }
+  }
+}
+
+template <int U>
+static void launch_rows_held(const float* x, const float* w, bf16* out, const int* rows_index, int rows, int n, float eps,
+                             cudaStream_t stream) {
+  gb_launch(rmsnorm_rows_held_kernel<U>, (rows + 3) / 4, 128, 0, stream, x, w, out, rows_index, rows, n, eps);
+}
+
 GB_EXPORT int gb_rmsnorm(const float* x, const float* w, void* out, int out_dtype, const int* rows_index, int rows,
                          int n, float eps, cudaStream_t stream) {
   if (rows <= 0) return 0;
   const int threads = n >= 1024 ? 256 : 128;
   if (out_dtype == GB_F32)
     gb_launch(rmsnorm_kernel<float>, rows, threads, 0, stream, x, w, (float*)out, rows_index, n, eps);
+  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 8)
+    launch_rows_held<8>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
+  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 16)
+    launch_rows_held<16>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
+  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 24)
+    launch_rows_held<24>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
+  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 32)
+    launch_rows_held<32>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
+  else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0 && n <= 32 * 4 * 40)
+    launch_rows_held<40>(x, w, (bf16*)out, rows_index, rows, n, eps, stream);
   else if (out_dtype == GB_BF16 && rows >= 512 && (n & 3) == 0)
     gb_launch(rmsnorm_rows_kernel, (rows + 7) / 8, 256, 0, stream, x, w, (bf16*)out, rows_index, rows, n, eps);
   else if (out_dtype == GB_BF16)

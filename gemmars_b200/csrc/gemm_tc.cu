@@ -78,7 +78,7 @@ struct QkvTail {
   const int2* token_place;  // prompts: [tokens] (page, position in the page) of each packed token
   NormLink link;            // any mode of gemm_tc_kernel: a norm taken into this product (all null: none)
 };
-enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3 };
+enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3, ST_TIMEOUT_PART = 4 };
 
 __device__ int g_status;   // first failure of any launch; 0 when all waits completed
 
@@ -729,13 +729,53 @@ __device__ __forceinline__ void tile_origin(int t, int tiles_m, int tiles_n, int
 }
 
 
+// The work of one CTA of the persistent kernel: tiles blockIdx.x, + gridDim.x, and so on.  Where
+// the last round of tiles would leave SMs idle, a product that adds into its result (`split` > 1)
+// cuts each tile of that round into `split` parts along the inner dimension, and the CTAs walk
+// those parts the same way, part 0 of every tile first: the CTAs stay in step along the inner
+// dimension, as they are in the whole rounds, so that what one fetches the others find in L2.
+// (Equal shares of all tiles' blocks laid end to end keep every SM as busy, but each CTA is then
+// at another place of the inner dimension: measured 6 % slower over a prompt of 8B layer sizes,
+// whose 100 MB of W and 50 MB of x in the down product no longer pass through L2 once.)
+struct TileWalk {
+  int t, kb0, kb1, part;   // the segment: blocks [kb0, kb1) of tile t; which part of the tile it is
+  int at, whole, last, split, kb_total;
+  __device__ __forceinline__ TileWalk(int tiles, int kb_total_, int split_) : at(blockIdx.x), split(split_), kb_total(kb_total_) {
+    whole = split > 1 ? tiles - tiles % (int)gridDim.x : tiles;   // tiles of the full rounds
+    last = tiles - whole;                                          // tiles of the round that is cut
+    set();
+  }
+  __device__ __forceinline__ void set() {
+    if (at < whole) {
+      t = at;
+      part = 0;
+      kb0 = 0;
+      kb1 = kb_total;
+    } else if (more()) {
+      const int p = at - whole;
+      part = p / last;
+      t = whole + p - part * last;
+      kb0 = (int)((long long)part * kb_total / split);
+      kb1 = (int)((long long)(part + 1) * kb_total / split);
+    }
+  }
+  __device__ __forceinline__ bool more() const { return at < whole + last * split; }
+  __device__ __forceinline__ bool shared() const { return at >= whole; }   // one of several parts of its tile
+  __device__ __forceinline__ void next() {
+    at += gridDim.x;
+    set();
+  }
+};
+
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
                           void* __restrict__ y, int M, int N, int K, long long ldy, int bn,
-                          const __grid_constant__ QkvTail tail) {
+                          const __grid_constant__ QkvTail tail, int split_last, int* __restrict__ part_flags) {
   constexpr bool GATED = MODE == EPI_SWIGLU_BF16;   // rows of a tile: 16 gate, 16 up, ... (see gate_rows)
+  // the last round's tiles in parts along the inner dimension: only where parts can be added
+  const int split = MODE == EPI_ACCUMULATE_F32 ? max(split_last, 1) : 1;
   constexpr bool QKV = MODE == EPI_QKV_BF16;        // a tile is one head: norm, rotation, cache write (qkv_prompt_round)
   constexpr int TILE_F = GATED ? BM / 2 : BM;       // features of the result per tile
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
@@ -795,10 +835,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       pdl_wait_prior();
       uint32_t it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x) {
+      for (TileWalk w(tiles, kb_total, split); w.more() && ok; w.next()) {
         int m0, n0;
-        tile_origin(t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        tile_origin(w.t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1)) {
             atomicCAS(&g_status, ST_OK, ST_TIMEOUT_EMPTY);
@@ -826,7 +866,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     if (lane == 0) {
       uint32_t it = 0, i = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++i) {
+      for (TileWalk w(tiles, kb_total, split); w.more() && ok; w.next(), ++i) {
         const uint32_t b = i & 1;
         if (i >= 2 && !mbar_wait(&acc_empty[b], ((i >> 1) - 1) & 1)) {   // the epilogue has read this buffer out
           atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
@@ -834,7 +874,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         }
         tc_fence_after();
         const uint32_t d = tmem + b * ACC_COLS;
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const uint32_t s = it % STAGES;
           if (!mbar_wait(&full_bar[s], (it / STAGES) & 1)) {
             atomicCAS(&g_status, ST_OK, ST_TIMEOUT_FULL);
@@ -846,7 +886,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           const uint64_t adesc = smem_desc(a), bdesc = smem_desc(a + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma(d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_mma(d, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, (kb > w.kb0 || k > 0) ? 1u : 0u);
           tc_commit(&empty_bar[s]);
         }
         tc_commit(&acc_full[b]);
@@ -864,10 +904,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
                                        (float*)((uint8_t*)tmem_slot + 16)};
     const bool both = bn % 32 == 0;   // 32 tokens per round; the result's map is cut to match
     uint32_t i = 0;
-    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++i) {
+    for (TileWalk w(tiles, kb_total, split); w.more(); w.next(), ++i) {
       const uint32_t b = i & 1;
       int m0, n0;
-      tile_origin(t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
+      tile_origin(w.t, tiles_m, tiles_n, bn, TILE_F, m0, n0);
       const int n = n0 + f;
       bool have = __all_sync(0xffffffffu, mbar_wait(&acc_full[b], (i >> 1) & 1));
       if (!have && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
@@ -878,7 +918,25 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       }
       if (!have) break;
       tc_fence_after();
-      const float bv = (bias && n < N) ? bias[n] : 0.f;
+      const float bv = (bias && n < N && w.kb0 == 0) ? bias[n] : 0.f;
+      // The parts of a tile are added in their order along the inner dimension, so that the sums
+      // have the same bits every run: a word per tile and warp counts the parts whose sums are in
+      // memory, part q adds when it reads q (its predecessors were walked earlier, or at the same
+      // time by CTAs that wait for nothing later than this one does), and the last part puts the
+      // word back to zero.
+      int* word = w.shared() ? part_flags + (w.t - w.whole) * 4 + warp : nullptr;
+      if (MODE == EPI_ACCUMULATE_F32 && word && w.part > 0) {
+        if (lane == 0) {
+          bool there = false;
+          for (uint32_t spin = 0; spin < WAIT_LIMIT && !there; ++spin) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+            there = v == w.part;
+          }
+          if (!there) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_PART);
+        }
+        __syncwarp();
+      }
       const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16) + b * ACC_COLS;
 #pragma unroll 1
       for (int c = 0; c < bn; c += both ? 32 : 16) {
@@ -928,6 +986,14 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[b]);
+      if (MODE == EPI_ACCUMULATE_F32 && word) {
+        if (lane == 0) {
+          tma_store_wait_all();    // this warp's sums are in memory
+          __threadfence();
+          asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(word), "r"(w.part + 1 < split ? w.part + 1 : 0) : "memory");
+        }
+        __syncwarp();
+      }
     }
     if (y_tma || QKV) tile_out.finish(lane);
   }
@@ -1025,7 +1091,8 @@ int launch_mode(int mode, const CUtensorMap& mw, const CUtensorMap& mx, const Ou
 
 template <int BN, int STAGES, int MODE>
 int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const float* bias, void* y, int M,
-                      int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
+                      int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream, const QkvTail& tail = QkvTail{},
+                      int* part_flags = nullptr) {
   // stages, 1 KB of barriers, the pieces on their way out, 1 KB to align the base
   constexpr size_t SMEM = (size_t)STAGES * ((size_t)BM * BK * 2 + BN * BK * 2) + 1024 + OUT_STAGING_BYTES + 1024;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
@@ -1039,8 +1106,29 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
     configured = true;
   }
   const int tiles = ((M + bn - 1) / bn) * ((N + TILE_F - 1) / TILE_F);
-  gb_launch(kernel, dim3(tiles < ctas ? tiles : ctas), dim3(THREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N,
-            K, ldy, bn, tail);
+  // Where the last round of tiles would leave SMs idle and TMA adds the sums into the result: that
+  // round's tiles in `split` parts along the inner dimension.  What a split costs, in blocks of the
+  // inner dimension: the rounds of parts it makes, and, since the parts of a tile add one after the
+  // other, a wait of about one tile's way out (its adds and their completion: about 9 blocks' time
+  // at 256 tokens) for every further part of the same tile that is walked in the same round.
+  int split = 1, grid = tiles < ctas ? tiles : ctas;
+  if (MODE == EPI_ACCUMULATE_F32 && part_flags && my.usable && tiles % ctas != 0) {
+    const int last = tiles % ctas, kb_total = (K + BK - 1) / BK;
+    const double way_out = 9.0 * bn / 256 + 1.0;
+    double best = 0.92 * kb_total;
+    for (int sp = 2; sp <= 8 && kb_total / sp >= 4; ++sp) {
+      const int rounds = (last * sp + ctas - 1) / ctas;
+      const int together = sp < (ctas + last - 1) / last ? sp : (ctas + last - 1) / last;   // parts of a tile in one round
+      const double cost = (double)rounds * kb_total / sp + (together - 1) * way_out + (rounds - 1) * 1.0;
+      if (cost < best) {
+        best = cost;
+        split = sp;
+      }
+    }
+    if (split > 1) grid = last * split < ctas && tiles < ctas ? last * split : ctas;
+  }
+  gb_launch(kernel, dim3(grid), dim3(THREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, bn, tail,
+            split, part_flags);
   return gb_launch_status();
 }
 
@@ -1156,9 +1244,13 @@ GB_EXPORT int gb_gemm_tc_qkv(const void* x, const void* w, const float* bias, vo
 
 // The same product for prompts (M > 64): one CTA per SM walks the tiles and the epilogue of a tile
 // runs under the MMAs of the next.  mode as gb_gemm_tc; bn: tokens per tile, a multiple of 16 up to
-// 256; ctas: CTAs to launch.
+// 256; ctas: CTAs to launch.  part_flags: null, or 4 * ctas int32 zeros: a product that adds into y
+// may then cut the tiles of a last round that is not full into parts along the inner dimension;
+// every launch leaves the words zero, and two launches that use the same words must not run at
+// the same time.
 GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* bias, void* y, int mode, int M, int N,
-                                    int K, long long ldx, long long ldy, int bn, int ctas, cudaStream_t stream) {
+                                    int K, long long ldx, long long ldy, int bn, int ctas, int* part_flags,
+                                    cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K % 8) || (ldx % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ctas <= 0) return GB_ERR_SIZE;
   if (bn < 16 || bn > 256 || (bn % 16)) return GB_ERR_SIZE;
@@ -1177,13 +1269,15 @@ GB_EXPORT int gb_gemm_tc_persistent(const void* x, const void* w, const float* b
     switch (mode) {
       case EPI_STORE_BF16: return launch_persistent<256, 4, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
       case EPI_STORE_F32: return launch_persistent<256, 4, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
-      case EPI_ACCUMULATE_F32: return launch_persistent<256, 4, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_ACCUMULATE_F32:
+        return launch_persistent<256, 4, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, part_flags);
     }
   } else {
     switch (mode) {
       case EPI_STORE_BF16: return launch_persistent<128, 6, EPI_STORE_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
       case EPI_STORE_F32: return launch_persistent<128, 6, EPI_STORE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
-      case EPI_ACCUMULATE_F32: return launch_persistent<128, 6, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream);
+      case EPI_ACCUMULATE_F32:
+        return launch_persistent<128, 6, EPI_ACCUMULATE_F32>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, QkvTail{}, part_flags);
     }
   }
   return GB_ERR_ARG;
@@ -1239,7 +1333,8 @@ GB_EXPORT int gb_gemm_tc_qkv_prompt(const void* x, const void* w, const float* b
   return launch_persistent<128, 6, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
 }
 
-// The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator).
+// The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator,
+// 4 the other part of a shared tile).
 // Synchronizes the device; for tests and health checks, not for the step.
 GB_EXPORT int gb_gemm_tc_status(int reset) {
   int v = -1;

@@ -413,10 +413,18 @@ def gemm_tc(x, w, out, bias=None, accumulate=False, bn=None, splits=None, stages
     return left
 
 
-def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=None):
+_part_flags = {}
+PERSISTENT_SPLIT_LAST_ROUND = True
+
+
+def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=None, ctas=None, split_last=None):
     """The tensor-core product for prompts (more than 64 rows of x): one CTA per SM walks the output
     tiles, and the epilogue of a tile runs while the next tile's MMAs fill the other accumulator
-    buffer.  Operands and modes as gemm_tc."""
+    buffer.  Operands and modes as gemm_tc.  Where the last round of tiles would leave SMs idle, a
+    product that adds into ``out`` cuts that round's tiles into parts along the inner dimension,
+    which are added in a fixed order (``split_last=False``: never)."""
+    if split_last is None:
+        split_last = PERSISTENT_SPLIT_LAST_ROUND
     _cuda(x, w, out, bias)
     m, k = x.shape
     n = w.shape[0] // 2 if swiglu else w.shape[0]
@@ -440,11 +448,18 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
         # SMs; a 2,048-token prompt of a 4B-shaped model took 20.5 ms against 18.4, of a 32B-shaped one
         # 35.3 ms against 30.9 over 16 layers)
         bn = 128 if m <= 128 else 256
+    ctas = ctas or sm_count(x.device)
+    flags = None
+    if accumulate and split_last:
+        # a word per tile of the last round and epilogue warp; zero between launches
+        flags = _part_flags.get(x.device.index)
+        if flags is None or flags.numel() < 4 * ctas:
+            flags = _part_flags[x.device.index] = torch.zeros(max(4 * ctas, 1024), dtype=torch.int32, device=x.device)
     f = _fn("gemm_tc", "gb_gemm_tc_persistent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
-             c_int, c_void_p])
+             c_int, c_void_p, c_void_p])
     _check(f(x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), mode, m, n, k, x.stride(0), out.stride(0), bn,
-             ctas or sm_count(x.device), _stream()), "gemm_tc_persistent", "matmul",
+             ctas, _ptr(flags), _stream()), "gemm_tc_persistent", "matmul",
            _nbytes(x, w, bias, out) + (_nbytes(out) if accumulate else 0))
 
 

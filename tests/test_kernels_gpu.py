@@ -119,7 +119,8 @@ def test_gemm_refuses_what_it_cannot_take(k):
         k.gemm_ref(x.cpu(), w.cpu(), out.cpu())
 
 
-@pytest.mark.parametrize("rows,n,eps", [(3, 80, 1e-5), (17, 4100, 1e-6)])
+@pytest.mark.parametrize("rows,n,eps", [(3, 80, 1e-5), (17, 4100, 1e-6), (515, 4096, 1e-6), (600, 2564, 1e-5),
+                                        (513, 5120, 1e-6), (512, 72, 1e-6), (514, 8200, 1e-6)])
 def test_rmsnorm_and_gather(k, rows, n, eps):
     torch.manual_seed(rows)
     x = torch.randn(rows + 4, n, device="cuda") * 3
@@ -401,6 +402,37 @@ def test_gemm_tc_persistent(k, m, n, kk, mode):
         out = torch.zeros(m, inter, device="cuda", dtype=torch.bfloat16)
         k.gemm_tc_persistent(x, wg, out, swiglu=True, bn=bn, ctas=ctas)
         assert (out.float() - want).abs().max().item() <= 2 ** -8 * want.abs().max().item() + 1e-6, (bn, ctas)
+    assert k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("m,n,kk", [(300, 520, 256), (515, 260, 2048), (1024, 1024, 1536), (700, 130, 72)])
+def test_gemm_tc_persistent_split_last_round(k, m, n, kk):
+    """A product that adds into its result and whose last round of tiles is not full: that round's
+    tiles are cut into parts along the inner dimension, and the CTAs that hold the parts of a tile
+    add them in order.  Against float32, against whole tiles, the same bits twice, and the words
+    that order the parts back at zero."""
+    torch.manual_seed(m + n)
+    x = (torch.randn(m, kk, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(n, kk, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(n, device="cuda")
+    base = torch.randn(m, n, device="cuda")
+    want = base + x.float() @ w.float().T + b
+    for bn in (128, 256):
+        tiles = -(-m // bn) * -(-n // 128)
+        for ctas in (2, 3, 5, 7, 11, 148):
+            outs = []
+            for _ in range(2):
+                out = base.clone()
+                k.gemm_tc_persistent(x, w, out, b, accumulate=True, bn=bn, ctas=ctas, split_last=True)
+                outs.append(out)
+            assert torch.equal(outs[0], outs[1]), (bn, ctas)
+            assert (outs[0] - want).abs().max().item() <= 1e-5 * want.abs().max().item() + 1e-6, (bn, ctas)
+            whole = base.clone()
+            k.gemm_tc_persistent(x, w, whole, b, accumulate=True, bn=bn, ctas=ctas, split_last=False)
+            assert (outs[0] - whole).abs().max().item() <= 1e-5 * want.abs().max().item() + 1e-6, (bn, ctas)
+            if tiles % ctas == 0 or kk < 2 * 4 * 64:
+                assert torch.equal(outs[0], whole)      # nothing to cut: the same walk
+    assert int(k._part_flags[x.device.index].abs().sum()) == 0
     assert k.gemm_tc_status() == 0
 
 
