@@ -19,6 +19,33 @@ __global__ void embed_gather_kernel(const W* __restrict__ table, const int* __re
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);  // ids are checked on the host; never read outside
   const W* row = table + (size_t)id * hidden;
   float* out = x + (size_t)t * hidden;
+  if (sizeof(W) == 2 && (hidden & 7) == 0 && (((uintptr_t)table | (uintptr_t)x) & 15) == 0) {
+    // 16 bytes of the row per load, all of a thread's loads asked for before the first is used: a
+    // decode step's few rows are a handful of round trips to memory, not one per two bytes
+    constexpr int U = 4;
+    const uint4* row8 = (const uint4*)row;
+    float4* out4 = (float4*)out;
+    const int n8 = hidden / 8;
+    for (int base = 0; base < n8; base += U * blockDim.x) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + threadIdx.x + u * blockDim.x;
+        v[u] = i < n8 ? row8[i] : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = base + threadIdx.x + u * blockDim.x;
+        if (i < n8) {
+          const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)&v[u].x), b = __bfloat1622float2(*(const __nv_bfloat162*)&v[u].y);
+          const float2 c = __bfloat1622float2(*(const __nv_bfloat162*)&v[u].z), d = __bfloat1622float2(*(const __nv_bfloat162*)&v[u].w);
+          out4[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+          out4[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
+        }
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[i] = to_f32(row[i]) * scale;
 }
 

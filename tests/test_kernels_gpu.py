@@ -143,6 +143,15 @@ def test_embedding_and_gated_activation(k):
     out = torch.empty(4, 72, device="cuda")
     k.embed_gather(table, tok, out, 1.5)
     assert torch.equal(out, table[tok.long()].float() * 1.5)
+    for hidden in (4096, 2568, 70):       # 16 bytes at a time, with an edge; rows that are not 16-byte aligned
+        table = torch.randn(301, hidden, device="cuda").bfloat16()
+        out = torch.empty(4, hidden, device="cuda")
+        k.embed_gather(table, tok, out, 0.75)
+        assert torch.equal(out, table[tok.long()].float() * 0.75)
+    table = torch.randn(301, 72, device="cuda")
+    out = torch.empty(4, 72, device="cuda")
+    k.embed_gather(table, tok, out, 1.0)
+    assert torch.equal(out, table[tok.long()])
     gu = torch.randn(5, 2 * 112, device="cuda")
     act = torch.empty(5, 112, device="cuda")
     k.silu_mul(gu, act)
