@@ -104,7 +104,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
                                long long out_stride, const int* __restrict__ page_table, int table_width, int nkv,
                                const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                const int* __restrict__ seq_slot, int ntok, int nh, int window, int skip_slot,
-                               int newest, float* __restrict__ part, int* __restrict__ prefix_out) {
+                               float* __restrict__ part, int* __restrict__ prefix_out) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* full_bar = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -155,22 +155,16 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
     }
-    // Row of the cache (page * nkv + kv head) of flat page p; its complement (negative) if the
-    // page holds one of the token's newest positions, which the kernel before this one may write.
-    auto lookup = [&](long long p) -> int {
+    auto lookup = [&](long long p) -> int {   // row of the cache (page * nkv + kv head) of flat page p
       if (p >= p1) return 0;
       const int t = token_of(prefix, ntok, nkv, p);
       const TokenSpan sp = token_span(t, tok_pos, tok_seq, seq_slot, window, skip_slot);
       const long long r = p - (long long)prefix[t] * nkv;
       const int kvh = (int)(r / sp.pages), page = (int)(r % sp.pages);
-      const int row = page_table[(size_t)sp.slot * table_width + (sp.first_page + page) % table_width] * nkv + kvh;
-      return (sp.first_page + page + 1) * KEYS > sp.hi - newest ? ~row : row;
+      return page_table[(size_t)sp.slot * table_width + (sp.first_page + page) % table_width] * nkv + kvh;
     };
     int next_row = lookup(p0 + lane);
-    // The first pages are asked for while the kernel before this one is still running, as long
-    // as they hold only positions of earlier steps and a stage is free without the consumers'
-    // help (they wait for that kernel before they touch q).
-    bool waited = false;
+    pdl_wait_prior();
     uint32_t it = 0;
     bool ok = true;
     for (long long base = p0; base < p1; base += 32) {
@@ -178,12 +172,7 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
       next_row = lookup(base + 32 + lane);
       const int n = (int)min((long long)32, p1 - base);
       for (int i = 0; i < n; ++i, ++it) {
-        const int coded = __shfl_sync(0xffffffffu, my_row, i);
-        const int row = coded < 0 ? ~coded : coded;
-        if (!waited && (coded < 0 || it >= STAGES)) {
-          pdl_wait_prior();
-          waited = true;
-        }
+        const int row = __shfl_sync(0xffffffffu, my_row, i);
         if (lane == 0 && ok) {
           const uint32_t s = it % STAGES;
           ok = it < STAGES || wait_or_abort(&empty_bar[s], ((it / STAGES) - 1) & 1, abort, 1);
@@ -198,7 +187,6 @@ attention_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const 
         __syncwarp();
       }
     }
-    if (!waited) pdl_wait_prior();       // never released before the kernel before this one is done
     if (lane == 0) pdl_release_next();   // the last page is on its way: the next kernel may move in
     __syncwarp();
     return;
@@ -542,11 +530,8 @@ static size_t stream_smem(int ntok, int rep) {
 // q, out: [ntok, nh * HD] bfloat16 (q rows 4-byte aligned).  kcache: [pages, nkv, 64, HD],
 // vcache: [pages, nkv, HD, 64], 16-byte aligned.  ctas: CTAs to launch (0: two per SM when they
 // fit, else one).  skip_slot: tokens of this slot belong to no sequence: nothing is read for them
-// and their rows of out are zero (-1: none).  newest: how many of a token's last positions the
-// kernel launched before this one may have written (1 in a decode step; pass a large number if
-// more of the cache may be that fresh): every other position has to be in the cache before that
-// kernel starts, since their pages are asked for while it is still running.  scratch: float32,
-// at least gb_attention_decode_stream_scratch(...) values.
+// and their rows of out are zero (-1: none).  scratch: float32, at least
+// gb_attention_decode_stream_scratch(...) values.
 GB_EXPORT long long gb_attention_decode_stream_scratch(int ntok, int nh, int nkv, int ctas) {
   if (nkv <= 0) return 0;
   return (long long)ctas * 2 * (nh / nkv) * (HD + 2) + ntok + 1;
@@ -556,8 +541,7 @@ GB_EXPORT int gb_attention_decode_stream(const void* q, long long q_stride, void
                                          const void* kcache, const void* vcache, long long pages,
                                          const int* page_table, int table_width, int page_size, int nkv, int hd,
                                          const int* tok_pos, const int* tok_seq, const int* seq_slot, int ntok, int nh,
-                                         int window, int skip_slot, int newest, int ctas, float* scratch,
-                                         cudaStream_t stream) {
+                                         int window, int skip_slot, int ctas, float* scratch, cudaStream_t stream) {
   if (ntok <= 0) return 0;
   if (hd != HD || page_size != KEYS || nkv <= 0 || nh % nkv || nh / nkv > 16 || ntok > MAX_TOKENS || ctas <= 0 || ctas > MAX_CTAS)
     return GB_ERR_SIZE;
@@ -579,7 +563,7 @@ GB_EXPORT int gb_attention_decode_stream(const void* q, long long q_stride, void
   int* prefix = (int*)(scratch + (size_t)ctas * 2 * rep * (HD + 2));
   gb_launch(attention_decode_stream_kernel, dim3(ctas), dim3(THREADS), smem, stream, mk, mv, (const bf16*)q, q_stride,
             (bf16*)out, out_stride, page_table, table_width, nkv, tok_pos, tok_seq, seq_slot, ntok, nh, window, skip_slot,
-            newest < 1 ? 1 : newest, part, prefix);
+            part, prefix);
   const int merge_threads = rep * HD >= 1024 ? 1024 : (rep * HD + 31) / 32 * 32;
   gb_launch(attention_decode_stream_merge_kernel, dim3(ntok * nkv), dim3(merge_threads), 0, stream, (bf16*)out, out_stride,
             (const float*)part, (const int*)prefix, tok_pos, tok_seq, seq_slot, window, skip_slot, ntok, nkv, nh, ctas);

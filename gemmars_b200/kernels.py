@@ -689,11 +689,6 @@ def attention_decode(q, out, nh, kcache, vcache, page_table, page_size, tok_pos,
 STREAM_DECODE_HEAD_DIMS = (64, 128)
 STREAM_DECODE_MAX_TOKENS = 4096
 _decode_stream_scratch = {}
-# Up to this many tokens the streaming kernel asks for its first pages while the kernel before it
-# is still running.  Measured inside replayed steps (8B layer sizes, context 8,192): batch 1
-# -2.3 %, 8 -0.9 %, 16 -1.0 %, 32 -0.6 %, 64 +1.0 % (there the small kernel before it, which
-# rotates and stores 64 tokens' heads, is slowed by 28 MB of pages on their way).
-STREAM_AHEAD_MAX_TOKENS = 32
 _outgrown = []
 
 
@@ -703,14 +698,12 @@ def attention_decode_stream_usable(ntok: int, nh: int, nkv: int, hd: int, page_s
 
 
 def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, tok_pos, tok_seq, seq_slot,
-                            window=None, ctas=None, skip_slot=None, cache_bytes: int = 0, newest=None):
+                            window=None, ctas=None, skip_slot=None, cache_bytes: int = 0):
     """bfloat16 attention of single positions with the cache streamed through shared memory by
     TMA: the pages that the step reads are dealt evenly to the CTAs as one flat list, whatever the
     lengths of the sequences; parts of a (token, kv head) that fall to different CTAs are added
     in key order by a second kernel.  Tokens of ``skip_slot`` (rows that pad a captured step) read
-    nothing and get zeros.  ``newest``: how many of a token's last positions the kernel launched
-    before this one may have written (a decode step: 1); the pages of all other positions are asked
-    for while that kernel is still running.  None: any position may be that fresh."""
+    nothing and get zeros."""
     _cuda(q, out, kcache, vcache, page_table, tok_pos, tok_seq, seq_slot)
     nkv, hd = kcache.shape[1], kcache.shape[3]
     ntok = q.shape[0]
@@ -723,7 +716,7 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
                           f"(at most {STREAM_DECODE_MAX_TOKENS}) not supported")
     defines = (("GB_HEAD_DIM", hd),)
     sig = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int,
-           c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+           c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     f = _fn("attention_decode_stream", "gb_attention_decode_stream", sig, defines=defines)
     if ctas is None:
         ctas = sm_count(q.device)   # one per SM; measured at 8,192 keys, batch 1 / 8 / 64: 17 / 54 / 323 us; two per SM: 24 / 58 / 329
@@ -737,7 +730,7 @@ def attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, t
     _check(f(q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), kcache.data_ptr(), vcache.data_ptr(),
              kcache.shape[0], page_table.data_ptr(), page_table.shape[1], page_size, nkv, hd, tok_pos.data_ptr(),
              tok_seq.data_ptr(), seq_slot.data_ptr(), ntok, nh, window or 0, -1 if skip_slot is None else skip_slot,
-             (1 << 30) if newest is None else newest, ctas, scratch.data_ptr(), _stream()),
+             ctas, scratch.data_ptr(), _stream()),
            "attention_decode_stream", "attention", _nbytes(q, out) + cache_bytes)
     count_launches(1)   # the merge kernel
 
@@ -904,8 +897,7 @@ def attention(ctx, q, out, nh, kcache, vcache, page_table, page_size, window=Non
         nkv = kcache.shape[1]
         if attention_decode_stream_usable(ctx.n_tokens, nh, nkv, kcache.shape[3], page_size):
             attention_decode_stream(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq,
-                                    ctx.seq_slot, window, skip_slot=ctx.pad_slot, cache_bytes=cached,
-                                    newest=ctx.max_new if ctx.n_tokens <= STREAM_AHEAD_MAX_TOKENS else None)
+                                    ctx.seq_slot, window, skip_slot=ctx.pad_slot, cache_bytes=cached)
             return
         shares = decode_shares(ctx.n_tokens, nh, nkv, ctx.max_total if window is None else min(ctx.max_total, window))
         attention_decode(q, out, nh, kcache, vcache, page_table, page_size, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot,
