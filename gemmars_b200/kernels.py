@@ -3,6 +3,10 @@
 Every function here works on CUDA tensors only and launches on PyTorch's current stream.  There
 is no CPU or library fallback: a tensor that is not on a CUDA device, or a unit that cannot be
 built, raises.
+
+Two kernels keep scratch memory per device between their launches (the decode attention's parts,
+the words that order the parts of a split prompt tile): work for one device is therefore launched
+on one stream at a time, as the engine does; two engines on one device take turns.
 """
 from __future__ import annotations
 
