@@ -580,6 +580,12 @@ def gemm_qkv_prompt(x, w, bias, q_out, nh, nkv, hd, q_weight, k_weight, eps, tab
            "gemm_qkv_prompt", "matmul", _nbytes(x, w, bias, q_out) + m * 2 * nkv * hd * 2)
 
 
+# 65 to 128 tokens (decoding above batch 64): a CTA per tile of 128 features x 128 tokens with both
+# accumulators, 96 CTAs at 8B layer sizes, takes 42 us with cold weights where the prompt kernel's
+# 192 tiles of 64 features take 54 (30.8 us of bytes); above 128 tokens the prompt kernel is ahead.
+GATED_TILE_128_MAX_TOKENS = 128
+
+
 def gemm_swiglu(x, w_gate_up, out):
     """out[M, N] = silu(x @ gate.T) * (x @ up.T) for w_gate_up = [gate; up] of 2N rows: one
     tensor-core kernel in bfloat16; two kernels (product, then activation) otherwise.  ``x`` may
@@ -591,8 +597,10 @@ def gemm_swiglu(x, w_gate_up, out):
             return
         x = link.materialize()
     if x.dtype == torch.bfloat16 and gemm_tc_usable(x, w_gate_up):
-        if x.shape[0] > 64:
+        if x.shape[0] > GATED_TILE_128_MAX_TOKENS:
             gemm_tc_persistent(x, w_gate_up, out, swiglu=True)
+        elif x.shape[0] > 64:
+            gemm_tc(x, w_gate_up, out, swiglu=True, bn=128, splits=1)
         else:
             gemm_tc(x, w_gate_up, out, swiglu=True)
         return
