@@ -303,9 +303,12 @@ struct PromptTailShared {
 
 // One round: tokens m_first .. m_first + 31 of head `head` (features 32 * warp + lane), the raw
 // products in x.  Queries leave through `tile_out`; keys and values go to the cache.
+// `warp`: which quarter of the head's features the warp holds (0 .. 3); `bar`: the named barrier of
+// the four warps that share the round.
 template <int MODE, int SLOT>
 __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[32], int head, int warp, int lane, int m_first,
-                                                 int M, int Nq, const PromptTailShared& sh, TileOut<MODE, SLOT>& tile_out) {
+                                                 int M, int Nq, const PromptTailShared& sh, TileOut<MODE, SLOT>& tile_out,
+                                                 int bar) {
   const int f = warp * 32 + lane;
   const bool is_q = head < tl.nh, is_k = !is_q && head < tl.nh + tl.nkv;
   // Asked for first, used last: where this lane's token (m_first + lane) lives in the cache, and
@@ -361,7 +364,7 @@ __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[3
 #pragma unroll
     for (int j = 0; j < 32; ++j) sq[j] = x[j] * x[j];
     sh.partial[warp * 32 + lane] = lanes_sum_32(sq, lane);     // token `lane`, this warp's 32 features
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
     const float total = sh.partial[lane] + sh.partial[32 + lane] + sh.partial[64 + lane] + sh.partial[96 + lane];
     const float inv = 1.0f / sqrtf(total / (float)BM + tl.eps), wf = w[f];
 #pragma unroll
@@ -373,7 +376,7 @@ __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[3
     const float* theirs = sh.exchange + (warp ^ 2) * 32 * 32;
 #pragma unroll
     for (int j = 0; j < 32; ++j) mine[j * 32 + lane] = x[j];
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       const float other = theirs[j * 32 + lane];
@@ -394,7 +397,7 @@ __device__ __forceinline__ void qkv_prompt_round(const QkvTail& tl, float (&x)[3
   }
   // With both steps on, the barrier of each keeps the other's memory safe for the next round;
   // with one alone, a warp could write the next round's values while another still reads these.
-  if ((w != nullptr) != (tl.rope_table != nullptr)) asm volatile("bar.sync 1, 128;" ::: "memory");
+  if ((w != nullptr) != (tl.rope_table != nullptr)) asm volatile("bar.sync %0, 128;" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -767,8 +770,14 @@ struct TileWalk {
   }
 };
 
+// The q/k/v mode has eight epilogue warps, two to each quarter of tensor memory's lanes (a warp
+// reaches the quarter warp % 4): warps 0-3 take the even rounds of 32 tokens of a tile, warps 6-9
+// the odd ones.  Its epilogue is work, not stores (a round is 2.9 us for four warps), and at
+// short inner dimensions (2,560: 16 us of MMAs a tile) it, not the MMAs, set the product's time.
+constexpr int PERSISTENT_QKV_THREADS = 320, QKV_STAGING_BYTES = 65 * 1024;   // pieces 32 KB, exchange 2 x 16 KB, sums 1 KB
+
 template <int BN, int STAGES, int MODE>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(MODE == EPI_QKV_BF16 ? PERSISTENT_QKV_THREADS : THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                           const __grid_constant__ CUtensorMap map_y, int y_tma, const float* __restrict__ bias,
                           void* __restrict__ y, int M, int N, int K, long long ldy, int bn,
@@ -796,10 +805,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   // gated: the pieces are 16 tokens of bfloat16 (1 KB), and the pairs' exchange has the upper half
   constexpr int SLOT = (GATED || QKV) ? OUT_STAGING_BYTES / 2 / (4 * PIECES) : PIECE_BYTES;
   static_assert(!GATED || (SLOT >= 16 * PIECE_FEATURES * 2 && OUT_STAGING_BYTES / 2 >= EXCHANGE_BYTES), "gated staging");
-  // q/k/v: bfloat16 pieces of 32 tokens in the lower half, the warps' exchange in the upper half,
-  // their partial sums behind the barriers
-  static_assert(!QKV || (SLOT >= PIECE_TOKENS * PIECE_FEATURES * 2 && OUT_STAGING_BYTES / 2 >= 4 * 32 * 32 * 4), "q/k/v staging");
-  static_assert((2 * STAGES + 4) * 8 + 16 + 4 * 32 * 4 <= 1024, "the barriers and the partial sums have 1 KB");
+  // q/k/v: eight warps' bfloat16 pieces of 32 tokens (32 KB), then each group of four warps' exchange
+  // (16 KB each), then their partial sums
+  static_assert(!QKV || (SLOT >= PIECE_TOKENS * PIECE_FEATURES * 2 && 8 * PIECES * SLOT == 32 * 1024), "q/k/v staging");
+  static_assert((2 * STAGES + 4) * 8 + 16 <= 1024, "the barriers have 1 KB");
+  constexpr int EPI_WARPS = QKV ? 8 : 4;
   __shared__ int epilogue_gave_up;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -813,7 +823,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);
+      mbar_init(&acc_empty[b], EPI_WARPS);
     }
     epilogue_gave_up = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -896,12 +906,13 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
   } else {
     // ---------------- epilogue warps: lane = feature, column = token
     pdl_wait_prior();
-    const int f = GATED ? (warp & 1) * 32 + lane : warp * 32 + lane;   // this lane's feature of the tile
+    const int quarter = warp & 3, group = warp >= 6 ? 1 : 0;          // group 1: the q/k/v mode's second four
+    const int f = GATED ? (warp & 1) * 32 + lane : quarter * 32 + lane;   // this lane's feature of the tile
     const bool is_up = GATED && warp >= 2;
-    TileOut<MODE, SLOT> tile_out(&map_y, out_staging, warp);
+    TileOut<MODE, SLOT> tile_out(&map_y, out_staging, group * 4 + quarter);
     GateExchange exchange(out_staging + OUT_STAGING_BYTES / 2, warp);
-    const PromptTailShared tail_shared{(float*)(out_staging + OUT_STAGING_BYTES / 2),
-                                       (float*)((uint8_t*)tmem_slot + 16)};
+    const PromptTailShared tail_shared{(float*)(out_staging + 32 * 1024 + group * 16 * 1024),
+                                       (float*)(out_staging + 64 * 1024) + group * 4 * 32};
     const bool both = bn % 32 == 0;   // 32 tokens per round; the result's map is cut to match
     uint32_t i = 0;
     for (TileWalk w(tiles, kb_total, split); w.more(); w.next(), ++i) {
@@ -913,7 +924,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       if (!have && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_TMEM);
       if (GATED || QKV) {   // the warps meet at barriers below: they leave together or not at all
         if (!have && lane == 0) epilogue_gave_up = 1;
-        asm volatile("bar.sync 3, 128;" ::: "memory");
+        asm volatile("bar.sync 3, %0;" ::"n"(EPI_WARPS * 32) : "memory");
         have = epilogue_gave_up == 0;
       }
       if (!have) break;
@@ -937,9 +948,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
         }
         __syncwarp();
       }
-      const uint32_t acc = tmem + ((uint32_t)(warp * 32) << 16) + b * ACC_COLS;
+      const uint32_t acc = tmem + ((uint32_t)(quarter * 32) << 16) + b * ACC_COLS;
 #pragma unroll 1
-      for (int c = 0; c < bn; c += both ? 32 : 16) {
+      for (int c = QKV ? 32 * group : 0; c < bn; c += QKV ? 64 : (both ? 32 : 16)) {
         if (m0 + c >= M) break;
         uint32_t v[16], v2[16];
         tc_ld16(acc + c, v);
@@ -975,7 +986,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
             x[j] = __uint_as_float(v[j]) + bv;
             x[16 + j] = __uint_as_float(v2[j]) + bv;
           }
-          qkv_prompt_round<MODE, SLOT>(tail, x, n0 / BM, warp, lane, m0 + c, M, tail.nh * BM, tail_shared, tile_out);
+          qkv_prompt_round<MODE, SLOT>(tail, x, n0 / BM, quarter, lane, m0 + c, M, tail.nh * BM, tail_shared, tile_out, 1 + group);
         } else if (y_tma) {
           tile_out.send(v, v2, both, bv, lane, n0 + warp * 32, m0 + c, N);
         } else {
@@ -1094,7 +1105,9 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
                       int N, int K, long long ldy, int bn, int ctas, cudaStream_t stream, const QkvTail& tail = QkvTail{},
                       int* part_flags = nullptr) {
   // stages, 1 KB of barriers, the pieces on their way out, 1 KB to align the base
-  constexpr size_t SMEM = (size_t)STAGES * ((size_t)BM * BK * 2 + BN * BK * 2) + 1024 + OUT_STAGING_BYTES + 1024;
+  constexpr size_t STAGING = MODE == EPI_QKV_BF16 ? QKV_STAGING_BYTES : OUT_STAGING_BYTES;
+  constexpr size_t SMEM = (size_t)STAGES * ((size_t)BM * BK * 2 + BN * BK * 2) + 1024 + STAGING + 1024;
+  constexpr int NTHREADS = MODE == EPI_QKV_BF16 ? PERSISTENT_QKV_THREADS : THREADS;
   static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
   static_assert((2 * STAGES + 4) * 8 + 16 <= 1024, "the barriers have 1 KB");
   constexpr int TILE_F = MODE == EPI_SWIGLU_BF16 ? BM / 2 : BM;
@@ -1127,7 +1140,7 @@ int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap
     }
     if (split > 1) grid = last * split < ctas && tiles < ctas ? last * split : ctas;
   }
-  gb_launch(kernel, dim3(grid), dim3(THREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, bn, tail,
+  gb_launch(kernel, dim3(grid), dim3(NTHREADS), SMEM, stream, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, bn, tail,
             split, part_flags);
   return gb_launch_status();
 }
@@ -1329,8 +1342,8 @@ GB_EXPORT int gb_gemm_tc_qkv_prompt(const void* x, const void* w, const float* b
   if (!my.usable) return GB_ERR_ARG;
   QkvTail tail{q_weight, k_weight, nullptr, nullptr, nullptr, nullptr, nullptr, (bf16*)kcache, (bf16*)vcache,
                eps, q_scale, nh, nkv, 1, page_size, (const float2*)rope_table, (const int2*)token_place};
-  if (bn > 128) return launch_persistent<256, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
-  return launch_persistent<128, 6, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
+  if (bn > 128) return launch_persistent<256, 3, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
+  return launch_persistent<128, 4, EPI_QKV_BF16>(mw, mx, my, bias, y, M, N, K, ldy, bn, ctas, stream, tail);
 }
 
 // The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator,
