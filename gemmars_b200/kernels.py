@@ -639,6 +639,8 @@ def check_status() -> None:
     for entry in _STATUS_ENTRIES:
         v = _status(entry, True)
         if v:
+            for flags in _part_flags.values():   # a kernel that gave up may have left a part's word set
+                flags.zero_()
             raise KernelError(f"{entry[3:-7]}: a bounded wait ran out on the device (code {v}); "
                               "the results computed since the last check are not valid")
 
