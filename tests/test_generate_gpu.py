@@ -62,6 +62,32 @@ def test_steps_launched_ahead_give_the_same_tokens(dtype, model_folders):
     assert any(reason == "stop" for _, reason in results["true"][0])
 
 
+def test_two_engines_take_turns_on_one_device(model_folders, tmp_path_factory):
+    """Two engines of different shapes on the same device, one after the other and again, each
+    with captured decode steps of its own: they share the kernels' per-device scratch and the
+    loaded units, and each still generates what it generates alone."""
+    from gemmars_b200 import Engine
+    from gemmars_b200.weights import write_random_model
+    small = model_folders(TINY_B)
+    wide_cfg = dict(TINY_B, hidden_size=256, num_attention_heads=16, num_key_value_heads=1, head_dim=64,
+                    intermediate_size=320, use_sliding_window=False, layer_types=["full_attention"] * TINY_B["num_hidden_layers"])
+    wide = str(tmp_path_factory.mktemp("wide"))
+    write_random_model(wide, wide_cfg, seed=9)
+    alone = {}
+    for name, folder, cfg in (("small", small, TINY_B), ("wide", wide, wide_cfg)):
+        eng = Engine.load(folder, "dtype=bfloat16;max_batch=4;max_tokens=4096")
+        alone[name] = [r.tokens for r in eng.generate(_prompts(cfg, [70, 9, 300, 33], seed=2), max_tokens=24)]
+        del eng
+    torch.cuda.empty_cache()
+    a = Engine.load(small, "dtype=bfloat16;max_batch=4;max_tokens=4096")
+    first = [r.tokens for r in a.generate(_prompts(TINY_B, [70, 9, 300, 33], seed=2), max_tokens=24)]     # captures its steps
+    b = Engine.load(wide, "dtype=bfloat16;max_batch=4;max_tokens=4096")
+    for _ in range(2):
+        assert [r.tokens for r in b.generate(_prompts(wide_cfg, [70, 9, 300, 33], seed=2), max_tokens=24)] == alone["wide"]
+        assert [r.tokens for r in a.generate(_prompts(TINY_B, [70, 9, 300, 33], seed=2), max_tokens=24)] == alone["small"]
+    assert first == alone["small"]
+
+
 def test_bfloat16_generation_runs_and_mostly_agrees(model_folders):
     from gemmars_b200 import Engine
     folder = model_folders(TINY_A)
