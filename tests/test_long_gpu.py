@@ -123,6 +123,52 @@ def test_prompts_cut_into_chunks_inside_one_step(sharp_model, mild_model, dtype,
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", TOL_BF16["B"])])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_random_schedules(sharp_model, mild_model, dtype, tol, graphs):
+    """Sequences that start at random steps, in slots that others have just given back, and move on
+    by random numbers of tokens (often one: a decode step, captured or not; sometimes a chunk
+    next to other sequences' single tokens), in batches of changing make-up, asking for logits at
+    random places: every row against the plain implementation of the same tokens whole.  What a
+    row's logits may not depend on is all varied at once: the cut into steps, the neighbours in
+    the batch, the slot and the pages."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, toks, ref = sharp_model if dtype == "float32" else mild_model
+    scale = float(np.abs(ref).max())
+    model = build_model(folder, dtype=dtype)
+    runner = Runner(model, max_tokens=64 * 40, max_batch=5, use_graphs=graphs)
+    rng = np.random.default_rng(17 + graphs)
+    # every sequence is a prefix of the same token string, so one plain forward pass serves all
+    live, started, checked = {}, 0, 0            # slot -> [fed, length]
+    for step in range(60):
+        while len(live) < 5 and started < 14 and rng.random() < 0.5:
+            live[runner.open()] = [0, int(rng.integers(1, 330))]
+            started += 1
+        if not live:
+            continue
+        single = rng.random() < 0.6               # a step of single tokens for all, or a mixed one
+        chosen = [s for s in live if rng.random() < 0.8] or [next(iter(live))]
+        items, expect = [], []
+        for s in chosen:
+            fed, length = live[s]
+            n = 1 if (single and fed > 0) else int(min(length - fed, rng.integers(1, 90)))
+            want = sorted(set(int(x) for x in rng.integers(0, n, size=rng.integers(0, 3)))) if not single else [0] if n == 1 else [n - 1]
+            items.append(StepItem(s, toks[fed:fed + n], want))
+            expect += [fed + w for w in want]
+            live[s][0] = fed + n
+        out = runner.step(items).cpu().numpy() if expect else runner.step(items)
+        for row, pos in zip(out if expect else [], expect):
+            assert np.abs(row - ref[pos]).max() <= tol * scale, (step, pos)
+            checked += 1
+        for s in [s for s in live if live[s][0] >= live[s][1]]:
+            runner.close(s)
+            del live[s]
+    assert started == 14 and checked > 60
+    for s in list(live):
+        runner.close(s)
+    assert runner.cache.pages_held() == 0
+
+
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-4), ("bfloat16", TOL_BF16["B"])])
 def test_a_batch_of_seventy_sequences(mild_model, dtype, tol):
     """More sequences than the decode kernels' 64-token tiles: the prompts in one step, then single
     tokens for all of them (replayed from a graph padded to 128 rows), then for the half that goes

@@ -116,6 +116,54 @@ def test_many_sequences_with_heads_of_128(small128, n_seqs, dtype, tol):
         assert kernels.attention_decode_stream_status() == 0 and kernels.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", TOL_BF16["S128"])])
+def test_random_schedules_with_heads_of_128(small128, dtype, tol):
+    """The random schedules of test_long_gpu.py at heads of 128, where the bfloat16 engine takes
+    other kernels (the streaming decode attention and its merge, the q/k/v product with the
+    per-head work in its epilogue, norms inside the decode products, the tensor-core prompt
+    attention): sequences start at random steps in slots just given back, move on by one token
+    (captured steps) or by chunks, beside changing neighbours; every wanted row against the plain
+    implementation of the same tokens whole."""
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    folder, pcfg, w = small128
+    rng = np.random.default_rng(23)
+    toks = rng.integers(0, SMALL_128["vocab_size"], 420).tolist()
+    ref = plain.forward(pcfg, w, toks)
+    scale = float(np.abs(ref).max())
+    runner = Runner(build_model(folder, dtype=dtype), max_tokens=64 * 48, max_batch=6)
+    live, started, checked = {}, 0, 0            # slot -> [fed, length]
+    for step in range(70):
+        while len(live) < 6 and started < 16 and rng.random() < 0.5:
+            live[runner.open()] = [0, int(rng.integers(1, 420))]
+            started += 1
+        if not live:
+            continue
+        single = rng.random() < 0.6
+        chosen = [s for s in live if rng.random() < 0.8] or [next(iter(live))]
+        items, expect = [], []
+        for s in chosen:
+            fed, length = live[s]
+            n = 1 if (single and fed > 0) else int(min(length - fed, rng.integers(1, 130)))
+            if single:
+                want = [n - 1]
+            else:
+                want = sorted(set(int(x) for x in rng.integers(0, n, size=rng.integers(0, 3))))
+            items.append(StepItem(s, toks[fed:fed + n], want))
+            expect += [fed + x for x in want]
+            live[s][0] = fed + n
+        out = runner.step(items)
+        for row, pos in zip(out.cpu().numpy() if expect else [], expect):
+            assert np.abs(row - ref[pos]).max() <= tol * scale, (step, pos)
+            checked += 1
+        for s in [s for s in live if live[s][0] >= live[s][1]]:
+            runner.close(s)
+            del live[s]
+    assert started == 16 and checked > 70
+    for s in list(live):
+        runner.close(s)
+    assert runner.cache.pages_held() == 0
+
+
 # ---------------------------------------------------------------------- a window's ring that wraps
 
 @pytest.fixture(scope="module")
