@@ -458,6 +458,8 @@ def gemm_tc_persistent(x, w, out, bias=None, accumulate=False, swiglu=False, bn=
         # a word per tile of the last round and epilogue warp; zero between launches
         flags = _part_flags.get(x.device.index)
         if flags is None or flags.numel() < 4 * ctas:
+            if flags is not None:
+                _outgrown.append(flags)       # a captured step may still point at it: never freed
             flags = _part_flags[x.device.index] = torch.zeros(max(4 * ctas, 1024), dtype=torch.int32, device=x.device)
     f = _fn("gemm_tc", "gb_gemm_tc_persistent",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_int,
