@@ -268,3 +268,53 @@ def test_released_width_bfloat16_against_float32():
     # the token either engine would pick is, in the other engine, within that bound of the best
     for g, r in zip(got, ref):
         assert r.max() - r[int(g.argmax())] <= TOL_BF16["S128"] * np.abs(ref).max()
+
+
+# hidden, query heads, kv heads, intermediate, tied head: the dense models of the family
+RELEASED = {"0.6b": (1024, 16, 8, 3072, True), "1.7b": (2048, 16, 8, 6144, True), "4b": (2560, 32, 8, 9728, True),
+            "14b": (5120, 40, 8, 17408, False), "32b": (5120, 64, 8, 25600, False)}
+
+
+@pytest.mark.parametrize("name", list(RELEASED))
+def test_released_layer_sizes_bfloat16_against_float32(name):
+    """The layer sizes of the other released dense models (two layers each, random weights, the
+    released vocabulary): widths that are no power of two, 40 heads, a hidden size smaller than
+    heads x head size, tied heads.  Two unequal prompts and single tokens for them, then 70
+    short prompts in one step and single tokens for 70, 40 and 20 of them (the prompt product
+    under a captured step of 128 rows, tiles of 64 and of 32 tokens): the bfloat16 engine against
+    the float32 engine on the same weights.  Measured: 0.8e-2 to 1.06e-2 of the largest logit."""
+    import torch
+    from gemmars_b200 import kernels
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    from gemmars_b200.weights import random_weights
+    h, nh, nkv, inter, tied = RELEASED[name]
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": h,
+           "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": 128, "intermediate_size": inter,
+           "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False,
+           "tie_word_embeddings": tied, "max_position_embeddings": 4096}
+    tensors = random_weights(cfg, seed=0, device="cuda:0")
+    rng = np.random.default_rng(0)
+    a, b = rng.integers(0, cfg["vocab_size"], 330).tolist(), rng.integers(0, cfg["vocab_size"], 75).tolist()
+    many = [rng.integers(0, cfg["vocab_size"], int(n)).tolist() for n in rng.integers(4, 90, 70)]
+    res = {}
+    for dtype in ("float32", "bfloat16"):
+        model = build_model(raw_config=cfg, tensors=tensors, dtype=dtype, device="cuda:0")
+        runner = Runner(model, max_tokens=64 * 200, max_batch=72)
+        sa, sb = runner.open(), runner.open()
+        rows = [runner.step([StepItem(sa, a[:300], [0, 150, 299]), StepItem(sb, b[:60], [59])]).float().cpu().numpy()]
+        for i in range(6):
+            rows.append(runner.step([StepItem(sa, [a[300 + i]], [0]), StepItem(sb, [b[60 + i]], [0])]).float().cpu().numpy())
+        slots = [runner.open() for _ in many]
+        rows.append(runner.step([StepItem(s, p[:-3], [len(p) - 4]) for s, p in zip(slots, many)]).float().cpu().numpy())
+        for n_live, back in ((70, 3), (40, 2), (20, 1)):
+            rows.append(runner.step([StepItem(s, [p[-back]], [0]) for s, p in list(zip(slots, many))[:n_live]]).float().cpu().numpy())
+        res[dtype] = np.concatenate(rows)
+        del runner, model
+    kernels.check_status()
+    ref, got = res["float32"], res["bfloat16"]
+    bound = 1.5e-2 * np.abs(ref).max()
+    assert np.abs(got - ref).max() <= bound
+    for g, r in zip(got, ref):
+        assert r.max() - r[int(g.argmax())] <= bound
+    del tensors
+    torch.cuda.empty_cache()
