@@ -31,6 +31,9 @@ SHAPES = {
     "8b": ("Qwen3-8B shape", qwen3_shape(36, 4096, 32, 8, 12288, False)),
     "4b": ("Qwen3-4B shape", qwen3_shape(36, 2560, 32, 8, 9728, True)),
     "32b": ("Qwen3-32B shape", qwen3_shape(64, 5120, 64, 8, 25600, False)),
+    "0.6b": ("Qwen3-0.6B shape", qwen3_shape(28, 1024, 16, 8, 3072, True)),
+    "1.7b": ("Qwen3-1.7B shape", qwen3_shape(28, 2048, 16, 8, 6144, True)),
+    "14b": ("Qwen3-14B shape", qwen3_shape(40, 5120, 40, 8, 17408, False)),
 }
 
 
