@@ -78,7 +78,7 @@ struct QkvTail {
   const int2* token_place;  // prompts: [tokens] (page, position in the page) of each packed token
   NormLink link;            // any mode of gemm_tc_kernel: a norm taken into this product (all null: none)
 };
-enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3, ST_TIMEOUT_PART = 4 };
+enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3, ST_TIMEOUT_PART = 4, ST_TIMEOUT_RECV = 5 };
 
 __device__ int g_status;   // first failure of any launch; 0 when all waits completed
 
@@ -424,6 +424,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_bar = empty_bar + STAGES;
   uint32_t* tmem_slot = (uint32_t*)(tmem_bar + 1);
+  uint64_t* recv_bar = tmem_bar + 2;             // the other ranks' partial sums for this rank's tokens have arrived
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * BN, n0 = blockIdx.y * BM;
@@ -438,6 +439,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(tmem_bar, 1);
+    mbar_init(recv_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 5) {
@@ -566,15 +568,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   }
   if (nsplit > 1) {
     // Every rank sends each token's partial sums to the rank that finishes the token, into that
-    // rank's shared memory (remote stores do not wait for an answer), and after one cluster
-    // barrier every rank adds what it received, in rank order, from its own shared memory.
+    // rank's shared memory (remote stores do not wait for an answer; each counts its bytes on the
+    // receiver's mbarrier), and a rank adds what it received, in rank order, from its own shared
+    // memory as soon as its own tokens' sums are all there: no second barrier of the cluster.
     // (Publishing in place and reading the other ranks' memory cost a round trip per token and a
     // second barrier before anyone could leave: 4.1 us from the last MMA to the last store with
     // eight ranks, measured inside a decode step.)  The memory is the pipeline's stages, so a rank
-    // may be written to only when its MMAs are done: that is the first barrier, which every
-    // thread arrives at as soon as this rank's accumulator is complete.
+    // may be written to only when its MMAs are done: that is the one barrier, which every
+    // thread arrives at as soon as this rank's accumulator is complete.  A rank may leave while
+    // its own sends are still on their way: they need nothing of the sender any more, and the
+    // receivers stay until everything they expect has arrived.
     float* recv = (float*)smem;   // [rank][token of this rank's share][accumulator][BM]
     constexpr int NACC = DUAL ? 2 : 1;
+    // what this rank will receive: every rank's 128 threads send one float per accumulator for each
+    // of this rank's tokens, and each float counts on recv_bar where it lands
+    if (threadIdx.x == 0) mbar_expect_tx(recv_bar, (uint32_t)(nsplit * (uint32_t)(c1 - c0) * NACC * BM * 4));
     cluster_arrive();
     cluster_wait();
     if (warp < 4) {
@@ -595,8 +603,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         for (int j = 0; j < 16; ++j) {
           if (c + j < real) {
             float* slot = recv + ((size_t)((int)split * share + local) * NACC) * BM + f;
-            st_peer_f32(slot, (uint32_t)owner, __uint_as_float(v[j]));
-            if (DUAL) st_peer_f32(slot + BM, (uint32_t)owner, __uint_as_float(u[j]));
+            st_peer_f32_counted(slot, (uint32_t)owner, __uint_as_float(v[j]), recv_bar);
+            if (DUAL) st_peer_f32_counted(slot + BM, (uint32_t)owner, __uint_as_float(u[j]), recv_bar);
             if (++local == share) {
               local = 0;
               ++owner;
@@ -605,8 +613,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
       }
     }
-    cluster_sync();
     if (warp < 4) {
+      // no barrier of the cluster: this rank goes on when its own tokens' sums are all there
+      if (!__all_sync(0xffffffffu, mbar_wait(recv_bar, 0)) && lane == 0) atomicCAS(&g_status, ST_OK, ST_TIMEOUT_RECV);
       const int f = warp * 32 + lane, n = n0 + f;
       const float out_g = (MODE == EPI_ACCUMULATE_F32 && link.out_weight && n < N) ? link.out_weight[n] : 0.f;
 #pragma unroll 1
@@ -1347,7 +1356,7 @@ GB_EXPORT int gb_gemm_tc_qkv_prompt(const void* x, const void* w, const float* b
 }
 
 // The status word: 0, or the first wait that ran out (1 operands, 2 free stage, 3 accumulator,
-// 4 the other part of a shared tile).
+// 4 the other part of a shared tile, 5 the other ranks' partial sums).
 // Synchronizes the device; for tests and health checks, not for the step.
 GB_EXPORT int gb_gemm_tc_status(int reset) {
   int v = -1;

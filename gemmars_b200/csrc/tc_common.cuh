@@ -121,6 +121,15 @@ __device__ __forceinline__ void st_peer_f32(float* local, uint32_t rank, float v
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+// The same, and the 4 bytes count on the mbarrier at `local_bar`'s place in that CTA: the receiver
+// waits for the bytes it expects instead of for a barrier of the whole cluster.
+__device__ __forceinline__ void st_peer_f32_counted(float* local, uint32_t rank, float v, uint64_t* local_bar) {
+  uint32_t addr, bar;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(bar) : "r"(smem_u32(local_bar)), "r"(rank));
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+               ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
+}
 // Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
 // groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
