@@ -77,6 +77,8 @@ struct QkvTail {
   const float2* rope_table; // prompts: [tokens][64] (cos, sin) of each packed token's angles, or null
   const int2* token_place;  // prompts: [tokens] (page, position in the page) of each packed token
   NormLink link;            // any mode of gemm_tc_kernel: a norm taken into this product (all null: none)
+  int recv_apart;           // gemm_tc_kernel with a split inner dimension: the ranks' partial sums arrive in
+                            // memory of their own behind the stages (see the exchange), not in the stages
 };
 enum { ST_OK = 0, ST_TIMEOUT_FULL = 1, ST_TIMEOUT_EMPTY = 2, ST_TIMEOUT_TMEM = 3, ST_TIMEOUT_PART = 4, ST_TIMEOUT_RECV = 5 };
 
@@ -432,6 +434,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb_total = (K + BK - 1) / BK;
   const int kb_begin = (int)((long long)kb_total * split / nsplit), kb_end = (int)((long long)kb_total * (split + 1) / nsplit);
   const int kb_count = kb_end - kb_begin;
+  // with the inner dimension split, every rank adds a share of the tile's real tokens over all ranks
+  const int real = min(M - m0, BN), share = (real + (int)nsplit - 1) / (int)nsplit;
+  const int c0 = min(real, (int)split * share), c1 = min(real, c0 + share);
+  // what this rank will receive then: every rank's 128 threads send one float per accumulator for
+  // each of this rank's tokens, and each float counts its bytes on recv_bar where it lands
+  const uint32_t recv_bytes = nsplit * (uint32_t)(c1 - c0) * (DUAL ? 2 : 1) * BM * 4;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -441,6 +449,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     mbar_init(tmem_bar, 1);
     mbar_init(recv_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (nsplit > 1) mbar_expect_tx(recv_bar, recv_bytes);
   }
   if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS));
@@ -450,6 +459,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  // With memory of its own for what the other ranks send, a rank may be written to at any time: all
+  // that the senders need is that its mbarrier exists, which this barrier of the cluster says, long
+  // before anyone has anything to send (its wait stands where the sending starts).
+  const bool recv_apart = nsplit > 1 && tail.recv_apart != 0;
+  if (recv_apart) cluster_arrive();
 
   if (warp == 4) {
     // ---------------- TMA producer
@@ -523,9 +537,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   // ---------------- epilogue (warps 0-3); the other warps wait at the barriers below
   bool have_acc = false;
-  // with the inner dimension split, every rank adds a share of the tile's real tokens over all ranks
-  const int real = min(M - m0, BN), share = (real + (int)nsplit - 1) / (int)nsplit;
-  const int c0 = min(real, (int)split * share), c1 = min(real, c0 + share);
   float bias_v = 0.f, old[8];
   __shared__ float row_scale[64], sq_part[4][32];
   const NormLink& link = tail.link;
@@ -578,12 +589,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // thread arrives at as soon as this rank's accumulator is complete.  A rank may leave while
     // its own sends are still on their way: they need nothing of the sender any more, and the
     // receivers stay until everything they expect has arrived.
-    float* recv = (float*)smem;   // [rank][token of this rank's share][accumulator][BM]
+    float* recv = recv_apart ? (float*)(smem + STAGES * STAGE_BYTES + 1024) : (float*)smem;   // [rank][token of this rank's share][accumulator][BM]
     constexpr int NACC = DUAL ? 2 : 1;
-    // what this rank will receive: every rank's 128 threads send one float per accumulator for each
-    // of this rank's tokens, and each float counts on recv_bar where it lands
-    if (threadIdx.x == 0) mbar_expect_tx(recv_bar, (uint32_t)(nsplit * (uint32_t)(c1 - c0) * NACC * BM * 4));
-    cluster_arrive();
+    if (!recv_apart) cluster_arrive();   // in the stages: not before every rank's MMAs have read them
     cluster_wait();
     if (warp < 4) {
       const int f = warp * 32 + lane;
@@ -1070,16 +1078,41 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const
            long long ldy, int splits, cudaStream_t stream, const QkvTail& tail = QkvTail{}) {
   constexpr int NW = MODE == EPI_SWIGLU_BF16 ? 2 : 1;
   constexpr size_t STAGE = (size_t)NW * BM * BK * 2 + BN * BK * 2;
-  constexpr size_t SMEM = (size_t)STAGES * STAGE + (2 * STAGES + 1) * 8 + 16 + 1024;
-  static_assert(SMEM <= 227 * 1024, "stages do not fit in shared memory");
+  constexpr size_t SMEM0 = (size_t)STAGES * STAGE + (2 * STAGES + 1) * 8 + 16 + 1024;
+  static_assert(SMEM0 <= 227 * 1024, "stages do not fit in shared memory");
+  // The ranks' partial sums in memory of their own (no barrier of the cluster before the exchange)
+  // where that costs no CTA an SM its place: [ranks][tokens a rank finishes][accumulators][128] floats
+  // behind the stages and their kilobyte of barriers.
+  size_t SMEM = SMEM0;
+  QkvTail tail_ = tail;
+  tail_.recv_apart = 0;
+  if (splits > 1 && BN <= 64) {
+    static int sms = 0;
+    if (!sms) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int real = M < BN ? M : BN, share = (real + splits - 1) / splits;
+    const size_t recv = (size_t)splits * share * NW * BM * 4, apart = (size_t)STAGES * STAGE + 2048 + recv;
+    const long long ctas = (long long)((M + BN - 1) / BN) * ((N + BM - 1) / BM) * splits;
+    const int wanted = (int)((ctas + sms - 1) / sms), fit_now = (int)(227 * 1024 / (SMEM0 + 1024)), fit_apart = (int)(227 * 1024 / (apart + 1024));
+    // ... and leaves half of an SM's shared memory to the CTAs of the next kernel, which start under
+    // this one's tail and ask for their first weights: with the memory of their own, 8B layer sizes
+    // at batch 1 got 3.5 % slower a step (two CTAs of 79 KB an SM), 0.6B sizes 4.2 % faster (one).
+    if (sms > 0 && fit_apart >= (wanted < fit_now ? wanted : fit_now) && (size_t)wanted * (apart + 1024) <= 114 * 1024) {
+      SMEM = apart;
+      tail_.recv_apart = 1;
+    }
+  }
   static_assert(BN > 64 || (size_t)NW * (BN + 8) * BM * 4 <= (size_t)STAGES * STAGE, "the ranks' partial sums need the stage memory");
   static_assert((size_t)OUT_STAGING_BYTES <= (size_t)STAGES * STAGE, "the pieces on their way out need the stage memory");
   auto kernel = gemm_tc_kernel<BN, STAGES, MODE>;
-  static bool configured = false;
-  if (!configured) {
+  static size_t configured = 0;
+  if (SMEM > configured) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM) != cudaSuccess)
       return (int)cudaGetLastError();
-    configured = true;
+    configured = SMEM;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((M + BN - 1) / BN, (N + BM - 1) / BM, splits);
@@ -1095,7 +1128,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const OutMap& my, const
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = GB_PDL ? 2 : 1;
-  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, tail);
+  return (int)cudaLaunchKernelEx(&cfg, kernel, mw, mx, my.map, my.usable, bias, y, M, N, K, ldy, tail_);
 }
 
 template <int BN, int STAGES>
