@@ -13,7 +13,7 @@ import torch
 
 import plain_qwen3 as plain
 from replay_util import Trace, run_trace
-from tiny_configs import SMALL_128, TINY_A, TINY_B, TOL_BF16
+from tiny_configs import SMALL_64, SMALL_128, TINY_A, TINY_B, TOL_BF16
 
 pytestmark = pytest.mark.gpu
 
@@ -116,8 +116,17 @@ def test_many_sequences_with_heads_of_128(small128, n_seqs, dtype, tol):
         assert kernels.attention_decode_stream_status() == 0 and kernels.gemm_tc_status() == 0
 
 
+@pytest.fixture(scope="module")
+def small64(tmp_path_factory):
+    from gemmars_b200.weights import write_random_model
+    folder = str(tmp_path_factory.mktemp("small64"))
+    write_random_model(folder, SMALL_64, seed=12)
+    return (folder,) + plain.load_folder(folder)
+
+
 @pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", TOL_BF16["S128"])])
-def test_random_schedules_with_heads_of_128(small128, dtype, tol):
+@pytest.mark.parametrize("heads", [128, 64])
+def test_random_schedules_with_heads_of_128_and_64(small128, small64, heads, dtype, tol):
     """The random schedules of test_long_gpu.py at heads of 128, where the bfloat16 engine takes
     other kernels (the streaming decode attention and its merge, the q/k/v product with the
     per-head work in its epilogue, norms inside the decode products, the tensor-core prompt
@@ -125,9 +134,9 @@ def test_random_schedules_with_heads_of_128(small128, dtype, tol):
     (captured steps) or by chunks, beside changing neighbours; every wanted row against the plain
     implementation of the same tokens whole."""
     from gemmars_b200.engine import Runner, StepItem, build_model
-    folder, pcfg, w = small128
+    folder, pcfg, w = small128 if heads == 128 else small64      # and at heads of 64, the kernels' other size
     rng = np.random.default_rng(23)
-    toks = rng.integers(0, SMALL_128["vocab_size"], 420).tolist()
+    toks = rng.integers(0, (SMALL_128 if heads == 128 else SMALL_64)["vocab_size"], 420).tolist()
     ref = plain.forward(pcfg, w, toks)
     scale = float(np.abs(ref).max())
     runner = Runner(build_model(folder, dtype=dtype), max_tokens=64 * 48, max_batch=6)

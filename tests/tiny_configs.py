@@ -42,6 +42,18 @@ SMALL_128 = {
     "layer_types": ["full_attention", "sliding_attention"],
 }
 
+# Heads of 64: the other head size that the tensor-core prompt attention and the streaming decode
+# attention take (three query heads to a kv head, no biases, a tied head).
+SMALL_64 = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 320, "vocab_size": 777, "rope_theta": 500000.0,
+    "rms_norm_eps": 1e-6, "attention_bias": False, "tie_word_embeddings": True,
+    "max_position_embeddings": 2048, "eos_token_id": 5,
+    "use_sliding_window": True, "sliding_window": 130,
+    "layer_types": ["sliding_attention", "full_attention"],
+}
+
 # How far the bfloat16 engine may be from the float64 plain implementation on the same
 # (bfloat16-valued) weights, as a fraction of the largest logit.  Measured on a B200 over three
 # weight seeds, sequences of 9 to 740 tokens, whole and with the last 32 tokens one by one: at
