@@ -109,20 +109,11 @@ __device__ __forceinline__ uint32_t cluster_size() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// A float to the same place in the shared memory of CTA `rank` of the cluster; visible there
-// after the next cluster barrier.
-__device__ __forceinline__ void st_peer_f32(float* local, uint32_t rank, float v) {
-  uint32_t addr;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-// The same, and the 4 bytes count on the mbarrier at `local_bar`'s place in that CTA: the receiver
-// waits for the bytes it expects instead of for a barrier of the whole cluster.
+// A float to the same place in the shared memory of CTA `rank` of the cluster, its 4 bytes counted
+// on the mbarrier at `local_bar`'s place in that CTA: the receiver waits for the bytes it expects
+// instead of for a barrier of the whole cluster.
 __device__ __forceinline__ void st_peer_f32_counted(float* local, uint32_t rank, float v, uint64_t* local_bar) {
   uint32_t addr, bar;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(addr) : "r"(smem_u32(local)), "r"(rank));
