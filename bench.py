@@ -383,7 +383,7 @@ def main():
     name, cfg = CONFIGS[args.config]
     layers_full = cfg["num_hidden_layers"]
     cfg = dict(cfg, num_hidden_layers=args.layers or layers_full)
-    # the three workloads of BASELINE.json; any other shape runs the 8B workload at its own sizes
+    # three shapes have workloads of their own; any other runs the 8B workload at its own sizes
     line = {"4b": run_4b, "32b": run_32b}.get(args.config, run_8b)(args, name, cfg, layers_full)
     print(json.dumps(line), flush=True)
     return 0
