@@ -173,6 +173,43 @@ def test_random_schedules_with_heads_of_128_and_64(small128, small64, heads, dty
     assert runner.cache.pages_held() == 0
 
 
+@pytest.mark.parametrize("hidden,heads,inter", [(4096, 32, 12288), (1024, 16, 3072)])
+def test_the_same_step_again_gives_the_same_bits(hidden, heads, inter):
+    """A decode step at released layer sizes (two layers; 1, 8 and 40 sequences of 1,000 cached
+    positions), taken back and run again 300 times: the logits are the same bits every time.  The
+    partial sums of a product's ranks, the parts of the attention and of a split prompt tile are
+    all added in a fixed order, whichever rank or CTA finishes first."""
+    from gemmars_b200 import kernels
+    from gemmars_b200.engine import Runner, StepItem, build_model
+    from gemmars_b200.weights import random_weights
+    cfg = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": hidden,
+           "num_attention_heads": heads, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": inter,
+           "vocab_size": 32000, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": False,
+           "tie_word_embeddings": False, "max_position_embeddings": 4096}
+    model = build_model(raw_config=cfg, tensors=random_weights(cfg, seed=1, device="cuda:0"), dtype="bfloat16", device="cuda:0")
+    for batch in (1, 8, 40):
+        runner = Runner(model, max_tokens=batch * 1100, max_batch=batch)
+        slots = [runner.open() for _ in range(batch)]
+        for s in slots:
+            runner.cache.extend(s, 1000)
+        runner.cache.sync()
+        for g in runner.cache.kv_groups:
+            g.k.normal_(0.0, 1.0)
+            g.v.normal_(0.0, 1.0)
+        first = None
+        for _ in range(300):
+            out = runner.step([StepItem(s, [11 + i], [0]) for i, s in enumerate(slots)])
+            for s in slots:
+                assert runner.cache.rollback(s, 1000)
+            if first is None:
+                first = out.clone()
+                assert torch.isfinite(first).all()
+            else:
+                assert torch.equal(out, first)
+        del runner
+    kernels.check_status()
+
+
 # ---------------------------------------------------------------------- a window's ring that wraps
 
 @pytest.fixture(scope="module")
