@@ -1,6 +1,6 @@
 """Measurements that the dispatch rules rest on, to be run again on another GPU or another width.
 
-    python -m gemmars_b200.tuning products [--shapes 4b,8b,32b] [--tokens 1,8,16,32,64]
+    python -m gemmars_b200.tuning products [--shapes 4b,8b,32b] [--tokens 1,8,16,32,64]      (shapes: 0.6b 1.7b 4b 8b 14b 32b)
     python -m gemmars_b200.tuning timeline --shape 8b --batch 8 --context 8192 [--layers 6] [--prompt 2048]
                                            [--temperature 0.7]
 
@@ -26,7 +26,7 @@ def qwen3_shape(layers, hidden, heads, kv_heads, inter, tied):
             "attention_bias": False, "tie_word_embeddings": tied, "max_position_embeddings": 40960}
 
 
-# The layer sizes of the released Qwen3 dense models that the measurements are taken at.
+# The layer sizes of the released Qwen3 dense models; the dispatch rules were measured at 4b, 8b and 32b.
 SHAPES = {
     "8b": ("Qwen3-8B shape", qwen3_shape(36, 4096, 32, 8, 12288, False)),
     "4b": ("Qwen3-4B shape", qwen3_shape(36, 2560, 32, 8, 9728, True)),
